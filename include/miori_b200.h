@@ -1,0 +1,146 @@
+/*
+ * miori_b200 -- C ABI of the B200 (sm_100a) backend for Miori's quantized-matmul path.
+ *
+ * This is the boundary a host program binds (C++, cgo, ctypes, ...).  Every entry
+ * returns 0 on success and a negative MIORI_E_* code on failure; the message for the
+ * calling thread's last failure is miori_last_error().  Nothing here allocates behind
+ * the caller's back except the buffer functions, and every launch entry only ENQUEUES
+ * work on the given CUDA stream (void* stream is a cudaStream_t; NULL is the legacy
+ * default stream), exactly as the reference's operators only encode dispatches
+ * (reference src/ops.cpp: every op ends in dispatchThreadgroups and returns void).
+ *
+ * Data formats (reference shaders/ops.metal:5-6,45 and src/cpu_ref.h:25-45):
+ *   q4  [N][K/8] uint32, eight 4-bit codes per word, low nibble first
+ *   q8  [N][K/4] uint32, four 8-bit codes per word, low byte first
+ *   s,b [N][K/group] bf16 scale and bias, weight = float(code)*scale + bias
+ *   x   [M][K] bf16 activations, y [M][N] fp32 (or bf16 with MIORI_OUT_BF16)
+ * group is 32 (what the reference hard-codes, config/m6.h:48) or 64.
+ *
+ * All pointers passed to launch entries are DEVICE pointers (or pointers the device
+ * can dereference, e.g. managed memory from miori_buffer_alloc(shared=1)).
+ */
+#ifndef MIORI_B200_H_
+#define MIORI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MIORI_OK 0
+#define MIORI_E_INVALID (-1)  /* bad argument: null pointer, unsupported shape, alignment */
+#define MIORI_E_CUDA (-2)     /* a CUDA runtime or driver call failed */
+#define MIORI_E_NOMEM (-3)    /* allocation failed */
+#define MIORI_E_STATE (-4)    /* call made in the wrong state */
+#define MIORI_E_DEVICE (-5)   /* a kernel reported an internal error (bounded wait expired) */
+
+/* launch flags */
+#define MIORI_OUT_F32 0u       /* y / C written as fp32 (what the reference's kernels write) */
+#define MIORI_OUT_BF16 1u      /* y / C rounded to bf16 (RNE) in the epilogue */
+#define MIORI_LAUNCH_PDL 2u    /* programmatic dependent launch: the kernel may start while its
+                                  predecessor on the stream drains; it prefetches weights (which
+                                  must be immutable while in flight) and waits for the
+                                  predecessor before touching x / A or writing y / C */
+#define MIORI_GEMV_EXACT 4u    /* force the fp32-dequant GEMV path for every M (default: M<=4) */
+
+const char* miori_last_error(void);
+/* Library version string, e.g. "miori_b200 0.1 sm_100a". */
+const char* miori_version(void);
+
+/* ---- device runtime: replaces reference src/metal.h:10-22 / src/metal.cpp ---------- */
+
+typedef struct miori_device miori_device; /* one GPU + one in-order queue (a CUDA stream) */
+typedef struct miori_buffer miori_buffer;
+
+/* Metal::init (src/metal.cpp:10-24): open GPU `ordinal`, create its queue. */
+int miori_device_open(int ordinal, miori_device** out);
+int miori_device_close(miori_device* dev);
+/* The queue's cudaStream_t, for passing to the launch entries. */
+void* miori_device_stream(miori_device* dev);
+int miori_device_ordinal(miori_device* dev);
+
+/* Metal::new_buffer (src/metal.cpp:42-48).  shared!=0: host-visible storage the host can
+ * read and write through miori_buffer_contents() with no explicit copy (CUDA managed
+ * memory, the counterpart of MTLResourceStorageModeShared); shared==0: device-only. */
+int miori_buffer_alloc(miori_device* dev, size_t bytes, int shared, miori_buffer** out);
+int miori_buffer_free(miori_buffer* buf);
+void* miori_buffer_contents(miori_buffer* buf);   /* MTL::Buffer::contents(); NULL if device-only */
+void* miori_buffer_device_ptr(miori_buffer* buf); /* pointer for launch entries */
+size_t miori_buffer_length(miori_buffer* buf);    /* MTL::Buffer::length() */
+/* Hint that the buffer will next be used by the GPU (1) or the host (0); optional. */
+int miori_buffer_prefetch(miori_buffer* buf, int to_device);
+
+/* Metal::begin / Metal::submit (src/metal.cpp:50-59).  begin opens a command scope on
+ * the queue; submit closes it and, when wait!=0, blocks until the queue drains and
+ * reports any asynchronous error. */
+int miori_begin(miori_device* dev);
+int miori_submit(miori_device* dev, int wait);
+
+/* Pinned host staging for callers that keep their own host buffers. */
+int miori_host_alloc(size_t bytes, void** out);
+int miori_host_free(void* p);
+/* Asynchronous copies on `stream` (host memory should be pinned). */
+int miori_memcpy_h2d(void* dst_dev, const void* src_host, size_t bytes, void* stream);
+int miori_memcpy_d2h(void* dst_host, const void* src_dev, size_t bytes, void* stream);
+int miori_stream_sync(void* stream);
+
+/* ---- GEMV: replaces shaders/ops.metal:6-42 (gemv4), :46-82 (gemv8),
+ *      shaders/batch.metal:145-188 (gemv4_b), :192-236 (gemv8_b) and the tuning variants
+ *      ops.metal:563-602 (gemv4x4), :711-751 (gemv4x2).  Bound by src/ops.cpp:7-37,
+ *      347-360, 376-390, 424-454, 524-574. ----------------------------------------- */
+
+/* y[m][n] = sum_k (code[n][k]*s[n][k/group] + b[n][k/group]) * x[m][k], 1 <= M <= 32.
+ * The result of a row m does not depend on M (reference shaders/batch.metal:142-144)
+ * within the same numeric path: M <= 4 dequantizes in fp32 (as gemv4 / gemv4_b do);
+ * M > 4 multiplies bf16-rounded weights on the tensor cores (as the reference does
+ * for wide batches through its bf16 cache, src/batch.cpp:223-230) unless
+ * MIORI_GEMV_EXACT is set.  Requires K % group == 0, group in {32,64}; q,s,b,x 16-byte
+ * aligned.  Only M rows of x are read and M rows of y written (the reference's
+ * gemv4_b always touches four, shaders/batch.metal:178-179). */
+int miori_gemv4(const void* q, const void* s, const void* b, const void* x, void* y,
+                uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
+                void* stream);
+int miori_gemv8(const void* q, const void* s, const void* b, const void* x, void* y,
+                uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
+                void* stream);
+
+/* ---- bf16 weight cache: replaces shaders/ops.metal:142-166 (dequant4), :754-779
+ *      (dequant8), shaders/gemm_mpp.metal:9-34 (dequant_tile).  Bound by
+ *      src/ops.cpp:74-87, 310-322, 624-637. ------------------------------------------ */
+
+/* out[n][k] = bf16(float(code)*scale + bias), row-major [N][K], bit-exact with
+ * src/cpu_ref.h:16-23,25-45. */
+int miori_dequant4_rowmajor(const void* q, const void* s, const void* b, void* out,
+                            uint32_t N, uint32_t K, uint32_t group, void* stream);
+int miori_dequant8_rowmajor(const void* q, const void* s, const void* b, void* out,
+                            uint32_t N, uint32_t K, uint32_t group, void* stream);
+/* The cache consumed by miori_gemm_bf16_cache.  Its layout is private to this library
+ * (as [N/64][K][64] is private to the reference's dequant_tile / gemm_mpp pair);
+ * miori_cache_bytes gives its size and miori_cache_to_rowmajor undoes the layout. */
+size_t miori_cache_bytes(uint32_t N, uint32_t K);
+int miori_dequant4_cache(const void* q, const void* s, const void* b, void* cache,
+                         uint32_t N, uint32_t K, uint32_t group, void* stream);
+int miori_cache_to_rowmajor(const void* cache, void* out, uint32_t N, uint32_t K,
+                            void* stream);
+
+/* ---- prefill GEMM: replaces shaders/gemm_mpp.metal:36-54 (gemm_mpp) and :57-73
+ *      (gemm_mpp32).  Bound by src/ops.cpp:324-345, 639-651. -------------------------- */
+
+/* C[M][N] = A[M][K] (bf16, contiguous) x cache(N,K)^T, fp32 accumulation on the
+ * tcgen05 tensor cores; C contiguous fp32 (or bf16 with MIORI_OUT_BF16).  One entry
+ * serves both reference tile shapes: a row of C does not depend on M
+ * (reference src/main.cpp:1403-1443).  Requires K % 64 == 0, N % 8 == 0, A and cache
+ * 16-byte aligned. */
+int miori_gemm_bf16_cache(const void* A, const void* cache, void* C, uint32_t M, uint32_t N,
+                          uint32_t K, uint32_t flags, void* stream);
+
+/* Non-zero if a kernel of this library recorded an internal error on the current
+ * device since the last call (bounded wait expired); clears the record. */
+int miori_device_error_poll(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIORI_B200_H_ */

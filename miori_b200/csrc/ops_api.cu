@@ -1,0 +1,98 @@
+// C ABI launch entries: argument validation, path selection, enqueue.
+#include "common.cuh"
+#include "dequant.cuh"
+#include "gemv_simt.cuh"
+
+using namespace miori_b200;
+
+namespace {
+
+int check_quant_args(const char* op, const void* q, const void* s, const void* b, uint32_t N,
+                     uint32_t K, uint32_t group) {
+    if (!q || !s || !b) return fail(MIORI_E_INVALID, "%s: null weight pointer", op);
+    if (group != 32 && group != 64)
+        return fail(MIORI_E_INVALID, "%s: group must be 32 or 64 (got %u)", op, group);
+    if (N == 0 || K == 0) return fail(MIORI_E_INVALID, "%s: empty shape N=%u K=%u", op, N, K);
+    if (K % group != 0)
+        return fail(MIORI_E_INVALID, "%s: K=%u is not a multiple of the group %u", op, K, group);
+    if (!aligned16(q) || !aligned16(s) || !aligned16(b))
+        return fail(MIORI_E_INVALID, "%s: q, s and b must be 16-byte aligned", op);
+    return MIORI_OK;
+}
+
+template <int BITS>
+int gemv_entry(const char* op, const void* q, const void* s, const void* b, const void* x, void* y,
+               uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream) {
+    int rc = check_quant_args(op, q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!x || !y) return fail(MIORI_E_INVALID, "%s: null activation pointer", op);
+    if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
+    if (!aligned16(x)) return fail(MIORI_E_INVALID, "%s: x must be 16-byte aligned", op);
+    if ((size_t)K * 2 * 4 > 200 * 1024)
+        return fail(MIORI_E_INVALID, "%s: K=%u too large for the activation staging", op, K);
+    return launch_gemv_simt<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
+}
+
+}  // namespace
+
+MIORI_API int miori_gemv4(const void* q, const void* s, const void* b, const void* x, void* y,
+                          uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
+                          void* stream) {
+    return gemv_entry<4>("miori_gemv4", q, s, b, x, y, N, K, M, group, flags, stream);
+}
+
+MIORI_API int miori_gemv8(const void* q, const void* s, const void* b, const void* x, void* y,
+                          uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
+                          void* stream) {
+    return gemv_entry<8>("miori_gemv8", q, s, b, x, y, N, K, M, group, flags, stream);
+}
+
+MIORI_API int miori_dequant4_rowmajor(const void* q, const void* s, const void* b, void* out,
+                                      uint32_t N, uint32_t K, uint32_t group, void* stream) {
+    int rc = check_quant_args("miori_dequant4_rowmajor", q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!out || !aligned16(out))
+        return fail(MIORI_E_INVALID, "miori_dequant4_rowmajor: out null or not 16-byte aligned");
+    return launch_dequant_rowmajor<4>(q, s, b, out, N, K, group, (cudaStream_t)stream);
+}
+
+MIORI_API int miori_dequant8_rowmajor(const void* q, const void* s, const void* b, void* out,
+                                      uint32_t N, uint32_t K, uint32_t group, void* stream) {
+    int rc = check_quant_args("miori_dequant8_rowmajor", q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!out || !aligned16(out))
+        return fail(MIORI_E_INVALID, "miori_dequant8_rowmajor: out null or not 16-byte aligned");
+    return launch_dequant_rowmajor<8>(q, s, b, out, N, K, group, (cudaStream_t)stream);
+}
+
+// The GEMM reads B through TMA as a K-major [N][K] bf16 matrix, so the cache is simply the
+// row-major dequantized tensor; the accessors keep the layout private to this library.
+MIORI_API size_t miori_cache_bytes(uint32_t N, uint32_t K) { return (size_t)N * K * 2; }
+
+MIORI_API int miori_dequant4_cache(const void* q, const void* s, const void* b, void* cache,
+                                   uint32_t N, uint32_t K, uint32_t group, void* stream) {
+    int rc = check_quant_args("miori_dequant4_cache", q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!cache || !aligned16(cache))
+        return fail(MIORI_E_INVALID, "miori_dequant4_cache: cache null or not 16-byte aligned");
+    return launch_dequant_rowmajor<4>(q, s, b, cache, N, K, group, (cudaStream_t)stream);
+}
+
+MIORI_API int miori_cache_to_rowmajor(const void* cache, void* out, uint32_t N, uint32_t K,
+                                      void* stream) {
+    if (!cache || !out) return fail(MIORI_E_INVALID, "miori_cache_to_rowmajor: null pointer");
+    MIORI_CUDA(cudaMemcpyAsync(out, cache, (size_t)N * K * 2, cudaMemcpyDeviceToDevice,
+                               (cudaStream_t)stream));
+    return MIORI_OK;
+}
+
+MIORI_API int miori_device_error_poll(void) {
+    unsigned int rec[4] = {0, 0, 0, 0};
+    if (cudaMemcpyFromSymbol(rec, g_device_error, sizeof(rec)) != cudaSuccess) return 0;
+    if (rec[0] == 0) return 0;
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_device_error, zero, sizeof(zero));
+    fail(MIORI_E_DEVICE, "kernel reported %u internal error(s); first code=%u detail=%u,%u", rec[0],
+         rec[1], rec[2], rec[3]);
+    return (int)rec[0];
+}

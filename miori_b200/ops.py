@@ -1,0 +1,89 @@
+"""Tensor-level wrappers over the C ABI.  torch is used for device memory and streams
+only; every computation happens in libmiori_b200.so."""
+from __future__ import annotations
+
+import torch
+
+from ._lib import OUT_BF16, check, lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_cuda:
+            raise ValueError("miori_b200 ops need CUDA tensors (there is no CPU path)")
+        if not t.is_contiguous():
+            raise ValueError("miori_b200 ops need contiguous tensors")
+
+
+def _gemv(fn, per_word, q, s, b, x, group, flags, out):
+    _need_cuda(q, s, b, x)
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    M, K = x.shape
+    N = q.shape[0]
+    if q.shape[1] * per_word != K:
+        raise ValueError(f"q has {q.shape[1]} words per row, expected {K // per_word}")
+    dt = torch.bfloat16 if flags & OUT_BF16 else torch.float32
+    y = out if out is not None else torch.empty((M, N), dtype=dt, device=x.device)
+    check(fn(q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), y.data_ptr(), N, K, M, group,
+             flags, _stream()))
+    return y
+
+
+def gemv4(q, s, b, x, group=32, flags=0, out=None):
+    """y[M][N] for packed 4-bit weights q[N][K/8] (int32 words), s/b[N][K/group] bf16."""
+    return _gemv(lib.miori_gemv4, 8, q, s, b, x, group, flags, out)
+
+
+def gemv8(q, s, b, x, group=32, flags=0, out=None):
+    """y[M][N] for packed 8-bit weights q[N][K/4] (int32 words)."""
+    return _gemv(lib.miori_gemv8, 4, q, s, b, x, group, flags, out)
+
+
+def _dequant(fn, per_word, q, s, b, group, out):
+    _need_cuda(q, s, b)
+    N, K = q.shape[0], q.shape[1] * per_word
+    o = out if out is not None else torch.empty((N, K), dtype=torch.bfloat16, device=q.device)
+    check(fn(q.data_ptr(), s.data_ptr(), b.data_ptr(), o.data_ptr(), N, K, group, _stream()))
+    return o
+
+
+def dequant4_rowmajor(q, s, b, group=32, out=None):
+    return _dequant(lib.miori_dequant4_rowmajor, 8, q, s, b, group, out)
+
+
+def dequant8_rowmajor(q, s, b, group=32, out=None):
+    return _dequant(lib.miori_dequant8_rowmajor, 4, q, s, b, group, out)
+
+
+def dequant4_cache(q, s, b, group=32, out=None):
+    """Layout-opaque bf16 cache for gemm_bf16_cache (returned as a flat bf16 tensor)."""
+    _need_cuda(q, s, b)
+    N, K = q.shape[0], q.shape[1] * 8
+    nbytes = lib.miori_cache_bytes(N, K)
+    o = out if out is not None else torch.empty(nbytes // 2, dtype=torch.bfloat16, device=q.device)
+    check(lib.miori_dequant4_cache(q.data_ptr(), s.data_ptr(), b.data_ptr(), o.data_ptr(), N, K,
+                                   group, _stream()))
+    return o
+
+
+def cache_to_rowmajor(cache, N, K):
+    _need_cuda(cache)
+    o = torch.empty((N, K), dtype=torch.bfloat16, device=cache.device)
+    check(lib.miori_cache_to_rowmajor(cache.data_ptr(), o.data_ptr(), N, K, _stream()))
+    return o
+
+
+def gemm_bf16_cache(A, cache, N, flags=0, out=None):
+    """C[M][N] = A[M][K] x cache(N,K)^T on the tcgen05 tensor cores."""
+    _need_cuda(A, cache)
+    M, K = A.shape
+    dt = torch.bfloat16 if flags & OUT_BF16 else torch.float32
+    Cm = out if out is not None else torch.empty((M, N), dtype=dt, device=A.device)
+    check(lib.miori_gemm_bf16_cache(A.data_ptr(), cache.data_ptr(), Cm.data_ptr(), M, N, K, flags,
+                                    _stream()))
+    return Cm

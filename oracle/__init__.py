@@ -1,0 +1,2 @@
+"""CPU oracle (test infrastructure).  Only tests/, __graft_entry__.smoke() and the
+CPU-baseline legs of bench.py may import this package."""
