@@ -1,4 +1,407 @@
-// placeholder until the tcgen05 GEMM lands
+// Prefill GEMM on the 5th-generation tensor cores: C[M][N] = A[M][K] * Bc[N][K]^T,
+// bf16 operands (both K-major), fp32 accumulation in tensor memory.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: 128-byte-swizzled [128 x 64] A and [BN x 64] B tiles into a
+//               STAGES-deep shared-memory ring (cp.async.bulk.tensor, mbarrier tx-count)
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16 per instruction)
+//               from shared-memory descriptors into one of two TMEM accumulators;
+//               tcgen05.commit releases ring slots and publishes finished accumulators
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (lane = row of C, column = column of
+//               C), convert, and store 128 contiguous bytes per thread; overlaps the next
+//               tile's main loop through the second accumulator
+// Tiles are visited in groups of 16 row blocks so that the A rows of a group and the
+// whole B matrix stay in L2.  Out-of-range rows/columns are zero-filled by TMA on load and
+// masked on store, so any M >= 1 and any N % 8 == 0 work with the same code; a row of C
+// therefore never depends on M (the reference's tile-shape invariance, src/main.cpp:1403-1443).
+// Every wait is bounded: on expiry the kernel records an error, drains and returns.
 #include "common.cuh"
+
+#include <cuda.h>
+
+namespace miori_b200 {
+namespace gemm {
+
+constexpr int BM = 128;       // rows of C per tile = UMMA M = TMEM lanes
+constexpr int BK = 64;        // bf16 per 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int GROUP_M = 16;   // row blocks per L2 group
+constexpr int THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // ~1 s
+
+template <int BN>
+struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulators (256 or 512: powers of two)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA is aborting (this or another role gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
+                                          uint32_t where) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort = 1u;
+            device_error(0x6E00u | where, blockIdx.x, parity);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, 8-row
+// atoms 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset
+    d |= (uint64_t)1 << 46;                      // version
+    d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D=f32, A=B=bf16, both K-major, shape 128 x BN.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t umma_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct TileCoord {
+    uint32_t m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t m_blocks, uint32_t n_blocks) {
+    const uint32_t per_group = GROUP_M * n_blocks;
+    const uint32_t group = t / per_group;
+    const uint32_t first_m = group * GROUP_M;
+    const uint32_t gm = min((uint32_t)GROUP_M, m_blocks - first_m);
+    const uint32_t r = t - group * per_group;
+    TileCoord c;
+    c.m_blk = first_m + r % gm;
+    c.n_blk = r / gm;
+    return c;
+}
+
+template <int BN, bool OUT_BF16>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cout,
+                         uint32_t M, uint32_t N, uint32_t K) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t raw = smem_addr(smem_raw);
+    const uint32_t tiles_base = (raw + 1023u) & ~1023u;            // 1024-byte aligned ring
+    const uint32_t bars = tiles_base + C::STAGES * C::STAGE_BYTES;  // barriers after the ring
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
+    const uint32_t tiles = m_blocks * n_blocks;
+    const uint32_t k_blocks = K / BK;
+
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0u;
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_addr(&tmem_base_slot)), "r"((uint32_t)C::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    pdl_wait_prior();  // A may be produced, and C read, by the preceding kernel
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 1))) break;
+                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                    const uint32_t sa = tiles_base + s * C::STAGE_BYTES;
+                    tma_load_2d(sa, &tmap_a, (int)(kb * BK), (int)(tc.m_blk * BM), full_bar(s));
+                    tma_load_2d(sa + C::A_BYTES, &tmap_b, (int)(kb * BK), (int)(tc.n_blk * BN),
+                                full_bar(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc<BN>();
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
+                const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+                if (!(ok = mbar_wait(tempty_bar(acc), aph ^ 1u, &abort_flag, 2))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                    if (!(ok = mbar_wait(full_bar(s), ph, &abort_flag, 3))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = tiles_base + s * C::STAGE_BYTES;
+                    const uint64_t adesc = umma_desc_sw128(sa);
+                    const uint64_t bdesc = umma_desc_sw128(sa + C::A_BYTES);
+#pragma unroll
+                    for (uint32_t k = 0; k < BK / UMMA_K; ++k) {
+                        // advance 32 bytes (16 bf16) inside the swizzled 128-byte row
+                        umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0u);
+                    }
+                    umma_commit(empty_bar(s));  // slot reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+            }
+        }
+    } else {
+        const uint32_t quad = warp & 3u;  // TMEM lane quadrant this warp may read
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
+            const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+            const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+            ok = mbar_wait(tfull_bar(acc), aph, &abort_flag, 4);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t row = tc.m_blk * BM + quad * 32u + lane;
+            const uint32_t col0 = tc.n_blk * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < (uint32_t)BN; c += 32u) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < M) {
+                    if (OUT_BF16) {
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(Cout) + (size_t)row * N + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (col0 + c + 8u * j < N) {
+                                uint4 v;
+                                v.x = float_to_bf16_bits(__uint_as_float(r[8 * j + 0])) |
+                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 1])) << 16);
+                                v.y = float_to_bf16_bits(__uint_as_float(r[8 * j + 2])) |
+                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 3])) << 16);
+                                v.z = float_to_bf16_bits(__uint_as_float(r[8 * j + 4])) |
+                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 5])) << 16);
+                                v.w = float_to_bf16_bits(__uint_as_float(r[8 * j + 6])) |
+                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 7])) << 16);
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+                            }
+                        }
+                    } else {
+                        float* dst = reinterpret_cast<float*>(Cout) + (size_t)row * N + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (col0 + c + 4u * j < N)
+                                *reinterpret_cast<uint4*>(dst + 4 * j) =
+                                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    // teardown: on abort give in-flight copies and MMAs time to land before freeing TMEM
+    __syncwarp();
+    if (abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows][K] bf16 row-major, box = [box_rows][64], 128-byte swizzle, zero fill out of range.
+static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
+                     uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return MIORI_OK;
+}
+
+template <int BN>
+static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N, uint32_t K,
+                       uint32_t flags, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    CUtensorMap ta, tb;
+    int rc = make_tmap(&ta, A, M, K, BM);
+    if (rc) return rc;
+    rc = make_tmap(&tb, Bc, N, K, BN);
+    if (rc) return rc;
+    const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    uint32_t grid = (uint32_t)sm_count();
+    if (grid > tiles) grid = tiles;
+    const bool bf16 = (flags & MIORI_OUT_BF16) != 0, pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    cudaError_t e;
+    if (bf16) {
+        auto kern = gemm_bf16_tcgen05_kernel<BN, true>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
+                       Cm, M, N, K);
+    } else {
+        auto kern = gemm_bf16_tcgen05_kernel<BN, false>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
+                       Cm, M, N, K);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05 launch");
+    return MIORI_OK;
+}
+
+}  // namespace gemm
+}  // namespace miori_b200
+
 using namespace miori_b200;
-MIORI_API int miori_gemm_bf16_cache(const void*, const void*, void*, uint32_t, uint32_t, uint32_t, uint32_t, void*) { return fail(MIORI_E_STATE, "miori_gemm_bf16_cache: not built yet"); }
+
+MIORI_API int miori_gemm_bf16_cache(const void* A, const void* cache, void* Cm, uint32_t M,
+                                    uint32_t N, uint32_t K, uint32_t flags, void* stream) {
+    if (!A || !cache || !Cm) return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: null pointer");
+    if (M == 0 || N == 0 || K == 0)
+        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: empty shape M=%u N=%u K=%u", M, N, K);
+    if (K % 64 != 0)
+        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: K=%u is not a multiple of 64", K);
+    if (N % 8 != 0)
+        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: N=%u is not a multiple of 8", N);
+    if (!aligned16(A) || !aligned16(cache) || !aligned16(Cm))
+        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: A, cache and C must be 16-byte aligned");
+    // Wide tiles amortise B traffic; narrow ones fill the SMs when there are few tiles.
+    const uint32_t m_blocks = (M + gemm::BM - 1) / gemm::BM;
+    const uint32_t tiles256 = m_blocks * ((N + 255) / 256);
+    const bool wide = tiles256 >= (uint32_t)sm_count() && !(flags & 0x100u);
+    if (wide || (flags & 0x200u))
+        return gemm::launch_gemm<256>(A, cache, Cm, M, N, K, flags, (cudaStream_t)stream);
+    return gemm::launch_gemm<128>(A, cache, Cm, M, N, K, flags, (cudaStream_t)stream);
+}
