@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200.
+
+Headline workload (BASELINE.json configs[2]): a synthetic 24-layer int4 stack, four
+projections per layer (2048->3072, 2048->2048, 2048->16384, 8192->2048), group-64 affine
+4-bit weights, evaluated at M in {1,2,4,8,16,32} activation rows.  One "step" is one pass of
+the GEMV path over the whole stack at each of the six M values (576 GEMV launches, six
+CUDA graphs with programmatic dependent launch).  `value` is effective HBM GB/s over the
+packed weight bytes streamed per step, inputs resident in HBM.  `e2e` is the same metric
+with host buffers: every pass copies its activations from pinned host memory and reads the
+last layer's outputs back, all through the C ABI.
+
+`--impl reference` times the reference's CPU arithmetic (oracle/_ref when group is 32 and it
+was built, else the C port in oracle/) on the host cores on a bounded sample.
+
+With torchrun (N>1) every projection is sharded by output rows N across ranks and each GEMV
+is followed by an NCCL all-gather of y (strong scaling: the total work is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = 24
+SHAPES = [(3072, 2048), (2048, 2048), (16384, 2048), (2048, 8192)]  # (N, K)
+M_SWEEP = [1, 2, 4, 8, 16, 32]
+GEMM_SHAPES = [(3072, 2048), (2048, 2048), (16384, 2048), (2048, 8192)]
+
+
+def packed_bytes(N, K, bits, group):
+    return N * K * bits // 8 + N * (K // group) * 4
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p, "measured"
+    except (OSError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# --------------------------------------------------------------------------- CPU arm
+
+def cpu_decode_sample(group, seconds=12.0):
+    """Time the CPU oracle on one layer of the stack at M=1, repeated for ~`seconds`."""
+    import numpy as np
+    import torch
+    from miori_b200 import synth
+    from oracle import oracle
+
+    ref = oracle.ref() if group == 32 else None
+    port = oracle.port()
+    kind = "reference" if ref is not None else "port"
+    eng = ref if ref is not None else port
+    cores = eng.threads()
+
+    def u16(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    layer = []
+    for i, (N, K) in enumerate(SHAPES):
+        q, s, b = synth.make_weight(N, K, 4, group, seed=100 + i)
+        x = synth.make_activation(1, K, seed=7)
+        layer.append((q.numpy().view(np.uint32), u16(s), u16(b), u16(x)))
+    nbytes = sum(packed_bytes(N, K, 4, group) for N, K in SHAPES)
+
+    def one_pass():
+        for q, s, b, x in layer:
+            if ref is not None:
+                ref.gemv(4, q, s, b, x)
+            else:
+                port.gemv(4, q, s, b, x, group)
+
+    one_pass()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        one_pass()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds or n >= 200:
+            break
+    gbs = nbytes * n / dt / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"{n} passes over one layer (4 projections, {nbytes} packed bytes) at M=1, "
+                      f"group {group}, double-precision dot of dequant4_elem as src/main.cpp:67-86",
+            "seconds": dt}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, t_all, vals = max(1, args.steps), 0.0, []
+    per_step = max(2.0, min(20.0, 90.0 / (steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_decode_sample(args.group, seconds=per_step / 2)
+    base = None
+    for _ in range(steps):
+        base = cpu_decode_sample(args.group, seconds=per_step)
+        vals.append(base["value"])
+        t_all += base["seconds"]
+    value = sum(vals) / len(vals)
+    base["value"] = value
+    out = {
+        "impl": "reference", "metric": "int4 GEMV effective HBM GB/s (M=1-32)", "value": value,
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * t_all / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64 accumulate over f32 dequant", "data": "synthetic",
+        "config": workload_config(args, 1), "cpu_baseline": base,
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out))
+
+
+def workload_config(args, world):
+    return {"workload": "decode_stack_int4: 24 layers x {2048->3072, 2048->2048, 2048->16384, "
+                        "8192->2048}, M in {1,2,4,8,16,32}", "group": args.group, "bits": 4,
+            "layers": LAYERS, "m_sweep": M_SWEEP, "out": "f32",
+            "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+            "l2": "inputs larger than L2 (821 MB of weights per pass)"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--group", type=int, default=64, choices=[32, 64])
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-pdl", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import miori_b200
+    from miori_b200 import synth
+    from miori_b200._lib import check, lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    G = args.group
+    pdl = 0 if args.no_pdl else miori_b200.LAUNCH_PDL
+
+    # ---- weights: every rank holds its row shard of every projection
+    stack = []
+    for l in range(LAYERS):
+        projs = []
+        for i, (N, K) in enumerate(SHAPES):
+            assert N % (16 * world) == 0
+            rows = N // world
+            q, s, b = synth.make_weight(N, K, 4, G, seed=1234 + l * 4 + i, device=dev)
+            sl = slice(rank * rows, (rank + 1) * rows)
+            projs.append((q[sl].contiguous(), s[sl].contiguous(), b[sl].contiguous()))
+            del q, s, b
+        stack.append(projs)
+    bytes_pass = LAYERS * sum(packed_bytes(N, K, 4, G) for N, K in SHAPES)  # whole job
+    MMAX = max(M_SWEEP)
+    x_dev = {M: [synth.make_activation(M, K, seed=50 + M, device=dev) for _, K in SHAPES] for M in M_SWEEP}
+    y_loc = {M: [torch.empty((M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
+    y_all = {M: [torch.empty((world, M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
+
+    def one_pass(M):
+        for projs in stack:
+            for (q, s, b), x, y, ya in zip(projs, x_dev[M], y_loc[M], y_all[M]):
+                miori_b200.gemv4(q, s, b, x, group=G, flags=pdl, out=y)
+                if world > 1:
+                    dist.all_gather_into_tensor(ya, y)
+
+    # ---- capture one CUDA graph per M
+    for M in M_SWEEP:
+        one_pass(M)
+    torch.cuda.synchronize()
+    graphs = {}
+    for M in M_SWEEP:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            one_pass(M)
+        graphs[M] = g
+    launches_pass = LAYERS * len(SHAPES)
+
+    def step():
+        for M in M_SWEEP:
+            graphs[M].replay()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    value = len(M_SWEEP) * bytes_pass / (ms_step * 1e-3) / 1e9
+
+    # ---- per-M breakdown (each M timed alone, same graphs)
+    per_m = {}
+    for M in M_SWEEP:
+        ms = timed(graphs[M].replay, max(3, args.steps // 2)) / max(3, args.steps // 2)
+        per_m[str(M)] = {"ms_per_pass": ms, "gbs": bytes_pass / (ms * 1e-3) / 1e9,
+                         "us_per_launch": 1e3 * ms / launches_pass}
+
+    # ---- e2e: host buffers through the C ABI, copies inside the timed region
+    stream = torch.cuda.current_stream().cuda_stream
+    h2d = d2h = 0
+    host_x, host_y = {}, {}
+    for M in M_SWEEP:
+        host_x[M] = [x.cpu().pin_memory() for x in x_dev[M]]
+        host_y[M] = [torch.empty((world, M, N // world)).pin_memory() if world > 1
+                     else torch.empty((M, N)).pin_memory() for N, _ in SHAPES]
+        h2d += sum(t.numel() * 2 for t in host_x[M])
+        d2h += sum(t.numel() * 4 for t in host_y[M])
+
+    def e2e_step():
+        for M in M_SWEEP:
+            for hx, dx in zip(host_x[M], x_dev[M]):
+                check(lib.miori_memcpy_h2d(dx.data_ptr(), hx.data_ptr(), hx.numel() * 2, stream))
+            graphs[M].replay()
+            srcs = y_all[M] if world > 1 else y_loc[M]
+            for hy, dy in zip(host_y[M], srcs):
+                check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
+            check(lib.miori_stream_sync(stream))  # the host consumes this pass's result
+
+    e2e_step()
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    e2e_val = len(M_SWEEP) * bytes_pass / (ms_e2e * 1e-3) / 1e9
+
+    peaks, peak_kind = measured_peaks()
+    m1 = per_m["1"]
+    roofline = {
+        "kernel": "gemv_mma_kernel<4,exact,1> (M=1 pass of the stack, 96 launches per pass)",
+        "bound": "hbm", "achieved": m1["gbs"] / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": m1["gbs"] / world / peaks["hbm_gbs"], "peak_kind": peak_kind,
+        "bytes_per_launch": bytes_pass / launches_pass / world,
+        "us_per_launch": m1["us_per_launch"], "traffic": None,
+    }
+    out = {
+        "metric": "int4 GEMV effective HBM GB/s (M=1-32)", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args, world),
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": args.steps * len(M_SWEEP) * launches_pass,
+        "per_m": per_m, "roofline": roofline, "clocks": clocks,
+    }
+
+    if rank == 0 and not args.no_extras and world == 1:
+        out["extras"] = extras(torch, miori_b200, synth, dev, G, peaks, timed)
+    if rank == 0 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_decode_sample(G, seconds=12.0)
+        out["cpu_baseline"].pop("seconds", None)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extras(torch, miori_b200, synth, dev, G, peaks, timed):
+    """Secondary measurements on one GPU: config 0 (rotating pool), config 1 (int8 head),
+    config 3 (prefill GEMM M=1024) and the cache build."""
+    ex = {}
+    flags = miori_b200.LAUNCH_PDL
+    # config 0: gemv4 M=1 K=2048 N=8192 over a rotating pool of 32 distinct matrices (302 MB > L2)
+    N, K = 8192, 2048
+    pool = [synth.make_weight(N, K, 4, G, seed=900 + i, device=dev) for i in range(32)]
+    x = synth.make_activation(1, K, seed=1, device=dev)
+    y = torch.empty((1, N), device=dev)
+    for q, s, b in pool:
+        miori_b200.gemv4(q, s, b, x, group=G, flags=flags, out=y)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for q, s, b in pool:
+            miori_b200.gemv4(q, s, b, x, group=G, flags=flags, out=y)
+    ms = timed(g.replay, 20) / 20
+    by = packed_bytes(N, K, 4, G)
+    ex["config0_gemv4_m1_n8192_k2048"] = {
+        "us_per_launch": 1e3 * ms / len(pool), "gbs": by * len(pool) / (ms * 1e-3) / 1e9,
+        "frac_of_hbm_peak": by * len(pool) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "how": "CUDA graph of 32 PDL launches over 32 distinct weight matrices (302 MB)"}
+    del pool
+    # config 1: gemv8 M=1 K=2048 N=131072
+    N, K = 131072, 2048
+    q, s, b = synth.make_weight(N, K, 8, G, seed=77, device=dev)
+    y = torch.empty((1, N), device=dev)
+    ms = timed(lambda: miori_b200.gemv8(q, s, b, x, group=G, out=y), 20) / 20
+    by = packed_bytes(N, K, 8, G)
+    ex["config1_gemv8_m1_n131072_k2048"] = {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
+                                            "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    del q, s, b
+    # config 3: prefill GEMM M=1024 on the bf16 cache + cache build
+    M = 1024
+    tot_flop, tot_ms, per = 0.0, 0.0, {}
+    for N, K in GEMM_SHAPES:
+        q, s, b = synth.make_weight(N, K, 4, G, seed=N + K, device=dev)
+        cache = miori_b200.dequant4_cache(q, s, b, group=G)
+        ms_c = timed(lambda: miori_b200.dequant4_cache(q, s, b, group=G, out=cache), 10) / 10
+        A = synth.make_activation(M, K, seed=3, device=dev)
+        Cm = torch.empty((M, N), device=dev)
+        ms = timed(lambda: miori_b200.gemm_bf16_cache(A, cache, N, out=Cm), 20) / 20
+        fl = 2.0 * M * N * K
+        per[f"N{N}_K{K}"] = {"us": 1e3 * ms, "tflops": fl / (ms * 1e-3) / 1e12,
+                             "cache_build_gbs": (packed_bytes(N, K, 4, G) + 2 * N * K) / (ms_c * 1e-3) / 1e9}
+        tot_flop += fl
+        tot_ms += ms
+        del q, s, b, cache, A, Cm
+    ex["config3_prefill_gemm_m1024"] = {
+        "tflops": tot_flop / (tot_ms * 1e-3) / 1e12, "frac_of_bf16_peak": tot_flop / (tot_ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "per_shape": per, "out": "f32"}
+    return ex
+
+
+if __name__ == "__main__":
+    main()

@@ -69,6 +69,58 @@ __device__ __forceinline__ void pdl_wait_prior() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// ---- shared-memory barriers (mbarrier) and bounded waits -------------------------------
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // ~1 s at boost clock
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA is aborting (this or another role gave up); on
+// expiry it raises the CTA's abort flag and records a device error with code `where`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
+                                          uint32_t where) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort = 1u;
+            device_error(0x6E00u | where, blockIdx.x, parity);
+            return false;
+        }
+    }
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
+// Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t v16) {
     return __uint_as_float(v16 << 16);
 }

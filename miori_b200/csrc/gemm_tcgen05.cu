@@ -16,8 +16,7 @@
 // therefore never depends on M (the reference's tile-shape invariance, src/main.cpp:1403-1443).
 // Every wait is bounded: on expiry the kernel records an error, drains and returns.
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tma_host.cuh"
 
 namespace miori_b200 {
 namespace gemm {
@@ -27,7 +26,6 @@ constexpr int BK = 64;        // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int GROUP_M = 16;   // row blocks per L2 group
 constexpr int THREADS = 192;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // ~1 s
 
 template <int BN>
 struct Cfg {
@@ -38,56 +36,6 @@ struct Cfg {
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulators (256 or 512: powers of two)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
 };
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false if the CTA is aborting (this or another role gave up).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
-                                          uint32_t where) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort = 1u;
-            device_error(0x6E00u | where, blockIdx.x, parity);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, 8-row
 // atoms 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
@@ -316,38 +264,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no libcuda link).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-                cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // [rows][K] bf16 row-major, box = [box_rows][64], 128-byte swizzle, zero fill out of range.
 static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
                      uint32_t box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
-    const cuuint64_t dims[2] = {K, rows};
-    const cuuint64_t strides[1] = {K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    return MIORI_OK;
+    return make_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, rows, BK, box_rows,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 template <int BN>

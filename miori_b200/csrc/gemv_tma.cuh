@@ -1,0 +1,537 @@
+// Weight-streaming GEMV with the weights staged through shared memory by TMA.
+//
+// One CTA per SM owns a contiguous range of 16-row tiles.  Each slab -- 16 rows x 1 KiB of
+// packed codes plus the rows' scales and biases, three cp.async.bulk.tensor requests -- goes
+// into a ring of shared-memory stages; completion is counted in bytes on a "full" mbarrier
+// per stage and consumers hand stages back through an "empty" mbarrier.  The ring is filled
+// BEFORE the kernel waits for its predecessor (programmatic dependent launch): weights are
+// immutable, so while kernel i reduces and stores, kernel i+1 already has its weights in
+// flight or resident and HBM stays busy across launch boundaries.  After the wait the CTA
+// stages x (see gemv_mma.cuh for the arithmetic and the k permutation).
+//
+// The 16 warps work in four independent groups of four; a group owns whole tiles, each of
+// its warps multiplies 4 of the 16 steps of a slab out of shared memory, and the four
+// partial sums per output are combined through shared memory behind a group-private named
+// barrier by a fixed shuffle tree (so a row's value does not depend on M).  There is no
+// CTA-wide barrier in the main loop.  A 17th warp is the TMA producer: one of its threads
+// refills a stage as soon as its group hands it back.  Out-of-range rows and columns are
+// zero-filled by TMA, which makes every code, scale and bias there contribute exactly 0.
+#pragma once
+#include "common.cuh"
+#include "gemv_mma.cuh"
+#include "tma_host.cuh"
+
+#include <algorithm>
+
+namespace miori_b200 {
+namespace gemvtma {
+
+constexpr int GROUPS = 4;                  // independent groups of 4 warps
+constexpr int WARPS = 4 * GROUPS;           // compute warps
+constexpr int THREADS = (WARPS + 1) * 32;  // plus one producer warp
+constexpr int MAX_STAGES = 12;
+constexpr int ROW_BYTES = 1024;            // packed bytes of one row in one slab
+constexpr int Q_BYTES = 16 * ROW_BYTES;
+constexpr int SB_BYTES = 16 * 128;         // scales (or biases) of 16 rows, up to 64 groups each
+constexpr int STAGE_BYTES = Q_BYTES + 2 * SB_BYTES;  // 20480
+// staged x in 16-byte units: the 4 chunks of a step sit at unit offsets 0,4,10,14 of an
+// 18-unit step and rows have an odd pitch, so the 8 lanes of a quarter warp (2 rows x 4
+// chunks) read 8 distinct bank groups with plain immediate offsets
+constexpr int STEP_UNITS = 18;
+constexpr int SLAB_X_BYTES = 16 * STEP_UNITS * 16;                 // staged x per k-slab and row
+constexpr int ZERO_BYTES = 3 * 4 * STEP_UNITS * 16 + 4 * 16 + 64;  // zeros read by masked lanes
+
+template <int MP>
+struct Red {
+    static constexpr int WS = 16 * MP + 1;           // padded stride of one warp's partials
+    static constexpr int GROUP_FLOATS = 2 * 4 * WS;  // double-buffered, 4 warps
+};
+
+__device__ __forceinline__ uint32_t shr_mulhi(uint32_t w, int k) {
+    // w >> k on the integer-multiply pipe, leaving the ALU pipe to the LOP3s
+    uint32_t r;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(1u << (32 - k)));
+    return r;
+}
+
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ uint32_t x_unit(uint32_t step, uint32_t t, uint32_t wd) {
+    return step * STEP_UNITS + 4u * t + 2u * (t >> 1) + wd;
+}
+
+// Stage x for the MMA B operand: permuted to the k order of the A fragments (plus 16*x for
+// 8-bit codes), laid out by x_unit(); for EXACT also the fp32 sum of x over every chunk.
+template <int BITS, bool EXACT, int MP>
+__device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, uint4* xs,
+                                               float* xsum, uint32_t M, uint32_t K,
+                                               uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
+    constexpr int CW = 128 / BITS, KU = BITS == 4 ? 8 : 4;
+    const uint32_t upr = steps_p * 16u;  // logical units per row
+    for (uint32_t i = threadIdx.x; i < (uint32_t)MP * upr; i += THREADS) {
+        const uint32_t m = i / upr, u = i - m * upr;
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (m < M && u * KU < K) {
+            if (BITS == 4) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
+                o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0,x4)
+                o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1,x5)
+                o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
+                o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3,x7)
+            } else {
+                const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + (size_t)m * K) + u);
+                const uint32_t x02 = __byte_perm(v.x, v.y, 0x5410);  // (x0,x2)
+                const uint32_t x13 = __byte_perm(v.x, v.y, 0x7632);  // (x1,x3)
+                const uint32_t sixteen = 0x41804180u, zero = 0u;     // bf16 16.0 pair
+                o.x = x02;
+                o.y = gemvmma::bf16x2_fma(x02, sixteen, zero);
+                o.z = x13;
+                o.w = gemvmma::bf16x2_fma(x13, sixteen, zero);
+            }
+        }
+        xs[(size_t)m * pitch + x_unit(u >> 4, (u >> 2) & 3u, u & 3u)] = o;
+    }
+    if (EXACT) {
+        const uint32_t chunks = K / CW;
+        for (uint32_t i = threadIdx.x; i < (uint32_t)MP * cpr; i += THREADS) {
+            const uint32_t m = i / cpr, c = i - m * cpr;
+            float sum = 0.0f;
+            if (m < M && c < chunks) {
+                const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c * CW);
+#pragma unroll
+                for (int j = 0; j < CW / 8; ++j) {
+                    const uint4 v = __ldg(xp + j);
+                    sum += bf16lo(v.x); sum += bf16hi(v.x); sum += bf16lo(v.y); sum += bf16hi(v.y);
+                    sum += bf16lo(v.z); sum += bf16hi(v.z); sum += bf16lo(v.w); sum += bf16hi(v.w);
+                }
+            }
+            xsum[i] = sum;
+        }
+    }
+}
+
+template <int BITS, bool EXACT, int NT, bool OUT_BF16>
+__global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1)
+gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                const __grid_constant__ CUtensorMap tmap_s,
+                const __grid_constant__ CUtensorMap tmap_b, const uint8_t* __restrict__ qlin,
+                const uint16_t* __restrict__ slin, const uint16_t* __restrict__ blin,
+                const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
+                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t dbg_skip) {
+    using namespace gemvmma;
+    const uint32_t nstage = ngrp * nsg;  // every active group owns a private ring of nsg stages
+    constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
+    constexpr int SK = 4 * CW;              // k per step
+    constexpr int KC = 16 * SK;             // k per slab: 16 steps, 4 per warp of a group
+    constexpr int MP = EXACT ? 2 * NT : 8 * NT;
+    constexpr float OFF = BITS == 4 ? 128.0f : 2176.0f;  // sum of the 128 offsets per code
+    constexpr uint32_t MASK = 0x000F000Fu, MAGIC = 0x43004300u;  // bf16 128.0 in both halves
+
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t grp = warp >> 2, wg = warp & 3u;
+    const uint32_t tiles = (N + 15u) >> 4;
+    const uint32_t kslabs = (K + KC - 1) / KC;
+    const uint32_t steps_p = kslabs * 16u;                 // padded steps along K
+    const uint32_t pitch = steps_p * STEP_UNITS + 1u;      // staged x row pitch (units, odd)
+    const uint32_t cpr = steps_p * 4u;                     // chunks per padded row
+    const uint32_t gps = KC >> gshift;                     // groups per slab row
+    // Linear mode (K fits one slab): the 16 rows of a tile are contiguous in memory, so a slab
+    // is three plain bulk copies and rows keep their global pitch in shared memory.  Otherwise
+    // rows are gathered by 2-D tiled TMA at a fixed 1 KiB / gps pitch.
+    const bool linear = qlin != nullptr;
+    const uint32_t chunks = K / CW, ng = K >> gshift;
+    const uint32_t qpitch = linear ? K * BITS / 8 : (uint32_t)ROW_BYTES;
+    const uint32_t spitch = linear ? ng : gps;
+
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bars[MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bars[MAX_STAGES];
+    __shared__ volatile uint32_t abort_flag;
+    uint8_t* ring = smem_raw;                                            // [nstage][STAGE_BYTES]
+    uint4* xs = reinterpret_cast<uint4*>(ring + (size_t)nstage * STAGE_BYTES);  // [MP][pitch]
+    uint4* zeros = xs + (size_t)MP * pitch;                              // ZERO_BYTES of zeros
+    float* xsum = reinterpret_cast<float*>(zeros + ZERO_BYTES / 16);     // [MP][cpr] (EXACT)
+    float* red = xsum + (EXACT ? (size_t)MP * cpr : 0);                  // [GROUPS] group areas
+
+    pdl_launch_dependents();
+
+    // This CTA's tiles.  Slabs are enumerated in sets of ngrp tiles (one
+    // per active group), k-slab major inside a set, so that consecutive slabs belong to
+    // different groups.  Group gi's k-th slab lives in stage gi*nsg + k % nsg: a stage is only
+    // ever waited on by one group, in order, so barrier parities are never ambiguous.
+    // tiles are dealt round-robin (tile = blockIdx.x + j*gridDim.x): at any moment the CTAs
+    // stream one contiguous window of the weight matrix, which HBM serves best
+    const uint32_t ntiles = (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const uint32_t total = ntiles * kslabs;
+        const uint32_t stage_tx = Q_BYTES + 2u * 16u * gps * 2u;  // bytes tiled TMA delivers per slab
+
+    // producer side (lane 0 of the producer warp only)
+    uint32_t issued = 0;
+    // Producer cursor, advanced incrementally (no divisions on the issue path): the next slab
+    // to issue is k-slab p_ks of the p_gi-th tile of the set starting at tile index p_set0;
+    // p_kmod = k % nsg and p_use = k / nsg for the owning group's slab counter k.
+    uint32_t p_set0 = 0, p_ks = 0, p_gi = 0, p_kmod = 0, p_use = 0;
+    // issue every slab whose stage is free, without blocking
+    auto try_refill = [&]() {
+        while (issued < total) {
+            const uint32_t stage = p_gi * nsg + p_kmod;
+            if (p_use != 0u) {
+                if (!mbar_try(smem_addr(&empty_bars[stage]), (p_use - 1u) & 1u)) break;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            const uint32_t bar = smem_addr(&full_bars[stage]);
+            const uint32_t dst = smem_addr(ring + (size_t)stage * STAGE_BYTES);
+            const uint32_t row = (blockIdx.x + (p_set0 + p_gi) * gridDim.x) * 16u;
+            if (linear) {
+                const uint32_t nrows = min(16u, N - row);  // rows past N keep stale (unused) data
+                mbar_expect_tx(bar, nrows * (qpitch + 4u * spitch));
+                bulk_g2s(dst, qlin + (size_t)row * qpitch, nrows * qpitch, bar);
+                bulk_g2s(dst + Q_BYTES, slin + (size_t)row * spitch, nrows * spitch * 2u, bar);
+                bulk_g2s(dst + Q_BYTES + SB_BYTES, blin + (size_t)row * spitch, nrows * spitch * 2u, bar);
+            } else {
+                mbar_expect_tx(bar, stage_tx);
+                tma_load_2d(dst, &tmap_q, (int)(p_ks * (ROW_BYTES / 4)), (int)row, bar);
+                tma_load_2d(dst + Q_BYTES, &tmap_s, (int)(p_ks * gps), (int)row, bar);
+                tma_load_2d(dst + Q_BYTES + SB_BYTES, &tmap_b, (int)(p_ks * gps), (int)row, bar);
+            }
+            ++issued;
+            // advance the cursor: next group of the set, then next k-slab, then next set
+            const uint32_t nt = min(ngrp, ntiles - p_set0);
+            if (++p_gi == nt) {
+                p_gi = 0;
+                if (++p_kmod == nsg) { p_kmod = 0; ++p_use; }
+                if (++p_ks == kslabs) { p_ks = 0; p_set0 += ngrp; }
+            }
+        }
+    };
+
+    const bool producer = threadIdx.x == WARPS * 32;
+    if (producer) {
+        abort_flag = 0u;
+        for (uint32_t i = 0; i < nstage; ++i) {
+            mbar_init(smem_addr(&full_bars[i]), 1);
+            mbar_init(smem_addr(&empty_bars[i]), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        try_refill();  // fills the rings: up to nstage slabs in flight before the wait
+    }
+
+    pdl_wait_prior();  // x (and y) belong to the predecessor until here
+
+    stage_x_padded<BITS, EXACT, MP>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+    for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
+        zeros[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+
+    // per-lane constants: byte offsets inside a stage and inside the staged x
+    const uint32_t n = lane >> 2;
+    const uint32_t sbrow = g * spitch;                            // bf16 index of row g's groups
+    const uint8_t* xb[NT];  // B-fragment base of this lane: k-slab 0, step wg
+    uint32_t xadv[NT];      // advance per k-slab (0 for masked lanes, which read zeros)
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const uint32_t m = EXACT ? (2u * j + (n & 1u)) : (8u * j + n);
+        const bool active = EXACT ? ((n >> 1) == t) : true;
+        xb[j] = active ? reinterpret_cast<const uint8_t*>(xs + (size_t)m * pitch + x_unit(wg, t, 0))
+                       : reinterpret_cast<const uint8_t*>(zeros);
+        xadv[j] = active ? (uint32_t)SLAB_X_BYTES : 0u;
+    }
+    const float* xsp = xsum + wg * 4u + t;  // chunk (ks*16 + i4*4 + wg)*4 + t of row 0
+    float* gred = red + (size_t)grp * Red<MP>::GROUP_FLOATS;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+
+    // `ok` turns false for good once a wait expires; the warp then skips waits and math but
+    // still takes part in every group barrier so that no other warp is left waiting.
+    bool ok = true;
+    uint32_t tile_it = 0;
+    uint32_t c_kmod = 0, c_par = 0;  // this group's slab counter k: k % nsg and (k / nsg) & 1
+    if (producer) {
+        // keep the rings fed until every slab has been issued (bounded: gives up with the CTA)
+        const long long t0 = clock64();
+        while (issued < total && !abort_flag) {
+            try_refill();
+            if (clock64() - t0 > 4 * WAIT_LIMIT_CYCLES) {
+                abort_flag = 1u;
+                device_error(0x6E14u, blockIdx.x, issued);
+            }
+        }
+    }
+    for (uint32_t set0 = 0; warp < WARPS && set0 < ntiles; set0 += ngrp) {
+        const uint32_t nt = min(ngrp, ntiles - set0);
+        if (grp >= nt) break;
+        const uint32_t tile = blockIdx.x + (set0 + grp) * gridDim.x;
+        for (uint32_t ks = 0; ks < kslabs; ++ks) {
+            const uint32_t stage = grp * nsg + c_kmod, parity = c_par;
+            if (++c_kmod == nsg) { c_kmod = 0; c_par ^= 1u; }
+            if (ok) {
+                ok = mbar_wait(smem_addr(&full_bars[stage]), parity, &abort_flag, 0x10);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+            }
+            if (ok && !dbg_skip) {
+                const uint8_t* st = ring + (size_t)stage * STAGE_BYTES;
+                const uint16_t* sp = reinterpret_cast<const uint16_t*>(st + Q_BYTES);
+                const uint16_t* bp = reinterpret_cast<const uint16_t*>(st + Q_BYTES + SB_BYTES);
+#pragma unroll 1
+                for (uint32_t i4 = 0; i4 < 4u; ++i4) {
+                    const uint32_t lc = (i4 * 4u + wg) * 4u + t;  // chunk inside the slab row
+                    // past the end of K (linear mode only; tiled TMA zero-fills): a zero scale
+                    // and bias against zero-staged x contribute exactly 0
+                    const bool valid = !linear || lc < chunks;
+                    const uint32_t lcc = valid ? lc : 0u;
+                    const uint4 q0 = *reinterpret_cast<const uint4*>(st + g * qpitch + lcc * 16u);
+                    const uint4 q1 = *reinterpret_cast<const uint4*>(st + (g + 8u) * qpitch + lcc * 16u);
+                    const uint32_t sbi = sbrow + ((lcc * CW) >> gshift);
+                    const uint32_t s0 = valid ? sp[sbi] : 0u, b0 = valid ? bp[sbi] : 0u;
+                    const uint32_t s1 = valid ? sp[sbi + 8u * spitch] : 0u;
+                    const uint32_t b1 = valid ? bp[sbi + 8u * spitch] : 0u;
+                    const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
+                    const uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
+                    // two independent accumulation chains (even / odd words)
+                    float d0[NT][4], d1[NT][4];
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        d0[j][0] = d0[j][1] = d0[j][2] = d0[j][3] = 0.0f;
+                        d1[j][0] = d1[j][1] = d1[j][2] = d1[j][3] = 0.0f;
+                    }
+                    uint32_t s2a = 0, b2a = 0, s2b = 0, b2b = 0;
+                    if (!EXACT) {
+                        s2a = s0 | (s0 << 16); b2a = b0 | (b0 << 16);
+                        s2b = s1 | (s1 << 16); b2b = b1 | (b1 << 16);
+                    }
+#pragma unroll
+                    for (int wd = 0; wd < 4; ++wd) {
+                        uint32_t a[4], c[4];  // pairs (n0,n4),(n1,n5),(n2,n6),(n3,n7), rows g, g+8
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            a[p] = lop3_and_or(p ? shr_mulhi(w0[wd], 4 * p) : w0[wd], MASK, MAGIC);
+                            c[p] = lop3_and_or(p ? shr_mulhi(w1[wd], 4 * p) : w1[wd], MASK, MAGIC);
+                            if (!EXACT) {
+                                a[p] = bf16x2_fma(bf16x2_sub(a[p], MAGIC), s2a, b2a);
+                                c[p] = bf16x2_fma(bf16x2_sub(c[p], MAGIC), s2b, b2b);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            const uint4 xu = *reinterpret_cast<const uint4*>(
+                                xb[j] + i4 * (4u * STEP_UNITS * 16u) + wd * 16);
+                            if (wd & 1) {
+                                mma_bf16(d1[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
+                                mma_bf16(d1[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
+                            } else {
+                                mma_bf16(d0[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
+                                mma_bf16(d0[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
+                            }
+                        }
+                    }
+                    if (EXACT) {
+                        const float sc0 = __uint_as_float(s0 << 16);
+                        const float bt0 = __fmaf_rn(-OFF, sc0, __uint_as_float(b0 << 16));
+                        const float sc1 = __uint_as_float(s1 << 16);
+                        const float bt1 = __fmaf_rn(-OFF, sc1, __uint_as_float(b1 << 16));
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            const float xs0 = xsp[(size_t)(2 * j) * cpr + i4 * 16u];
+                            const float xs1 = xsp[(size_t)(2 * j + 1) * cpr + i4 * 16u];
+                            acc[j][0] = __fmaf_rn(sc0, d0[j][0] + d1[j][0], __fmaf_rn(bt0, xs0, acc[j][0]));
+                            acc[j][1] = __fmaf_rn(sc0, d0[j][1] + d1[j][1], __fmaf_rn(bt0, xs1, acc[j][1]));
+                            acc[j][2] = __fmaf_rn(sc1, d0[j][2] + d1[j][2], __fmaf_rn(bt1, xs0, acc[j][2]));
+                            acc[j][3] = __fmaf_rn(sc1, d0[j][3] + d1[j][3], __fmaf_rn(bt1, xs1, acc[j][3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < NT; ++j)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) acc[j][e] += d0[j][e] + d1[j][e];
+                    }
+                }
+            }
+            if (ok) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_addr(&empty_bars[stage]));  // stage consumed
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) xb[j] += xadv[j];
+            xsp += 64;
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) xb[j] -= (size_t)kslabs * xadv[j];
+        xsp -= (size_t)kslabs * 64;
+
+        // ---- tile complete: quad sum (EXACT), then 4 partials per output through shared memory
+        constexpr int WS = Red<MP>::WS;
+        float* buf = gred + (size_t)(tile_it & 1u) * 4 * WS;
+        float* mine = buf + (size_t)wg * WS;
+        if (EXACT) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = acc[j][e];
+                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                    acc[j][e] = v;
+                }
+            if (t == 0) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    mine[g * MP + 2 * j] = acc[j][0];
+                    mine[g * MP + 2 * j + 1] = acc[j][1];
+                    mine[(g + 8) * MP + 2 * j] = acc[j][2];
+                    mine[(g + 8) * MP + 2 * j + 1] = acc[j][3];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                mine[g * MP + 8 * j + 2 * t] = acc[j][0];
+                mine[g * MP + 8 * j + 2 * t + 1] = acc[j][1];
+                mine[(g + 8) * MP + 8 * j + 2 * t] = acc[j][2];
+                mine[(g + 8) * MP + 8 * j + 2 * t + 1] = acc[j][3];
+            }
+        }
+        named_barrier(1u + grp, 128u);
+        const uint32_t gt = wg * 32u + lane;  // thread index inside the group
+#pragma unroll
+        for (uint32_t base = 0; base < 16u * MP * 4u; base += 128u) {
+            const uint32_t idx = base + gt;
+            const uint32_t o = idx >> 2, w = idx & 3u;  // output o = m*16 + r, partial of warp w
+            const uint32_t r = o & 15u, m = o >> 4;
+            float v = buf[(size_t)w * WS + r * MP + m];
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+            const uint32_t row = tile * 16u + r;
+            if (w == 0 && m < M && row < N && ok) {
+                if (OUT_BF16)
+                    reinterpret_cast<uint16_t*>(y)[(size_t)m * N + row] = (uint16_t)float_to_bf16_bits(v);
+                else
+                    reinterpret_cast<float*>(y)[(size_t)m * N + row] = v;
+            }
+        }
+        ++tile_it;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    }
+
+    if (abort_flag) {  // let copies still in flight land before the CTA's memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+    }
+}
+
+template <int BITS, bool EXACT, int NT>
+size_t fixed_smem(uint32_t K) {
+    constexpr int KC = 16 * 4 * (128 / BITS);
+    constexpr int MP = EXACT ? 2 * NT : 8 * NT;
+    const uint32_t kslabs = (K + KC - 1) / KC, steps_p = kslabs * 16;
+    size_t bytes = (size_t)MP * (steps_p * STEP_UNITS + 1) * 16 + ZERO_BYTES;
+    if (EXACT) bytes += (size_t)MP * steps_p * 4 * 4;
+    bytes += (size_t)GROUPS * Red<MP>::GROUP_FLOATS * 4;
+    return bytes;
+}
+
+// Ring plan for this problem: active groups and stages per group; ngrp == 0 means the TMA
+// path cannot take it.
+struct Plan {
+    uint32_t ngrp, nsg;
+};
+template <int BITS, bool EXACT, int NT>
+Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
+    constexpr int KC = 16 * 4 * (128 / BITS);
+    Plan p = {0, 0};
+    if ((K / group) % 8 != 0) return p;  // scale rows must have a 16-byte pitch for TMA
+    const size_t fixed = fixed_smem<BITS, EXACT, NT>(K);
+    const uint32_t tiles = (N + 15) / 16, kslabs = (K + KC - 1) / KC;
+    const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)sm_count());
+    const uint32_t tiles_cta = (tiles + grid - 1) / grid;  // tiles of the busiest CTA
+    // aim at half an SM so that two consecutive kernels can be resident together; settle for
+    // one CTA per SM when the staged activations are large
+    // one CTA per SM when the staged activations are large, or when the CTA streams many more
+    // slabs than half an SM can hold (a long kernel gains nothing from sharing the SM, and a
+    // saturated HBM needs ~100 KB in flight per SM)
+    const size_t target = 112 * 1024, hard = 208 * 1024;
+    uint32_t st = 0;
+    if (fixed + 4 * STAGE_BYTES <= target) st = (uint32_t)((target - fixed) / STAGE_BYTES);
+    if (st == 0 || tiles_cta * kslabs > 2 * st) {
+        if (fixed + 2 * STAGE_BYTES > hard) return p;
+        st = (uint32_t)((hard - fixed) / STAGE_BYTES);
+    }
+    p.ngrp = std::min<uint32_t>(std::min<uint32_t>(GROUPS, st), tiles_cta);
+    const uint32_t sets = (tiles_cta + p.ngrp - 1) / p.ngrp;
+    p.nsg = std::min<uint32_t>(st / p.ngrp, sets * kslabs);  // no more than a group ever needs
+    if (p.ngrp * p.nsg > (uint32_t)MAX_STAGES) p.nsg = MAX_STAGES / p.ngrp;
+    return p;
+}
+
+template <int BITS, bool EXACT, int NT>
+int launch_one(Plan plan, const void* q, const void* s, const void* b, const void* x, void* y,
+               uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
+               cudaStream_t stream) {
+    constexpr int KC = 16 * 4 * (128 / BITS);
+    const size_t smem = fixed_smem<BITS, EXACT, NT>(K) + (size_t)plan.ngrp * plan.nsg * STAGE_BYTES;
+    const uint32_t tiles = (N + 15u) / 16u;
+    const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)sm_count());
+    const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    const uint32_t gshift = group == 32 ? 5u : 6u;
+    // K within one slab: plain bulk copies (rows of a tile are contiguous); else tiled TMA
+    const bool linear = K <= (uint32_t)KC && !(flags & 0x2000u);
+    CUtensorMap tq, ts, tb;
+    int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)K * BITS / 32, N,
+                          ROW_BYTES / 4, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tmap_2d(&ts, s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, K / group, N, KC / group, 16,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, K / group, N, KC / group, 16,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const uint8_t* ql = linear ? reinterpret_cast<const uint8_t*>(q) : nullptr;
+    cudaError_t e;
+#define MIORI_TMA_LAUNCH(OB)                                                                     \
+    do {                                                                                         \
+        auto kern = gemv_tma_kernel<BITS, EXACT, NT, OB>;                                        \
+        e = cudaSuccess;                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e == cudaSuccess)                                                                    \
+            e = launch(kern, dim3(grid), dim3(THREADS), smem, stream, pdl, tq, ts, tb, ql,       \
+                       reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
+                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg,  \
+                       (flags & 0x1000u) ? 1u : 0u);        \
+    } while (0)
+    if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true); else MIORI_TMA_LAUNCH(false);
+#undef MIORI_TMA_LAUNCH
+    if (e != cudaSuccess) return cuda_fail(e, "gemv_tma launch");
+    return MIORI_OK;
+}
+
+// Try the TMA path; returns 1 if this problem is not eligible (nothing launched).
+template <int BITS>
+int try_launch(const void* q, const void* s, const void* b, const void* x, void* y, uint32_t N,
+               uint32_t K, uint32_t M, uint32_t group, uint32_t flags, cudaStream_t stream) {
+    Plan pl;
+#define MIORI_TMA_TRY(EX, NTV)                                                                   \
+    do {                                                                                         \
+        pl = plan_stages<BITS, EX, NTV>(N, K, group);                                            \
+        if (pl.ngrp == 0) return 1;                                                              \
+        return launch_one<BITS, EX, NTV>(pl, q, s, b, x, y, N, K, M, group, flags, stream);      \
+    } while (0)
+    if (M <= 2) MIORI_TMA_TRY(true, 1);
+    if (M <= 4) MIORI_TMA_TRY(true, 2);
+    if constexpr (BITS == 8) {
+        return 1;
+    } else {
+        if (M <= 8) MIORI_TMA_TRY(false, 1);
+        if (M <= 16) MIORI_TMA_TRY(false, 2);
+        MIORI_TMA_TRY(false, 4);
+    }
+#undef MIORI_TMA_TRY
+}
+
+}  // namespace gemvtma
+}  // namespace miori_b200

@@ -1,7 +1,9 @@
 // C ABI launch entries: argument validation, path selection, enqueue.
 #include "common.cuh"
 #include "dequant.cuh"
+#include "gemv_mma.cuh"
 #include "gemv_simt.cuh"
+#include "gemv_tma.cuh"
 
 using namespace miori_b200;
 
@@ -28,6 +30,17 @@ int gemv_entry(const char* op, const void* q, const void* s, const void* b, cons
     if (!x || !y) return fail(MIORI_E_INVALID, "%s: null activation pointer", op);
     if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
     if (!aligned16(x)) return fail(MIORI_E_INVALID, "%s: x must be 16-byte aligned", op);
+    const bool force_exact = (flags & MIORI_GEMV_EXACT) != 0;
+    const bool force_simt = (flags & 0x400u) != 0;  // tuning override: shape-agnostic SIMT path
+    const bool no_bulk = (flags & 0x800u) != 0;     // tuning override: register-streaming kernel
+    if (!force_simt && !(force_exact && M > 4)) {
+        if (!no_bulk) {
+            rc = gemvtma::try_launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
+            if (rc <= 0) return rc;  // launched (0) or failed (<0); 1 = not eligible
+        }
+        if (gemvmma::supported<BITS>(K, M, force_exact))
+            return gemvmma::launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
+    }
     if ((size_t)K * 2 * 4 > 200 * 1024)
         return fail(MIORI_E_INVALID, "%s: K=%u too large for the activation staging", op, K);
     return launch_gemv_simt<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);

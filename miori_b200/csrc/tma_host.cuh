@@ -1,0 +1,59 @@
+// Host-side construction of TMA tensor maps (cuTensorMapEncodeTiled) without linking
+// libcuda: the entry point comes from the CUDA runtime.
+#pragma once
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace miori_b200 {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Row-major 2-D tensor [rows][inner] of `dtype` elements (`esize` bytes each), box
+// [box_rows][box_inner], zero fill outside the tensor.  The row pitch inner*esize must be a
+// multiple of 16 bytes and the base 16-byte aligned.
+inline int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
+                        uint32_t esize, uint64_t inner, uint64_t rows, uint32_t box_inner,
+                        uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {inner * esize};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return MIORI_OK;
+}
+
+#ifdef __CUDACC__
+// 2-D tiled TMA load into shared memory; c0 is the innermost (element) coordinate, whose
+// byte offset must be a multiple of 16.  Completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+#endif
+
+}  // namespace miori_b200

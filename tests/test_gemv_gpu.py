@@ -90,10 +90,23 @@ def test_rows_do_not_depend_on_m():
     for m in range(4):
         y1 = _run(4, q, s, b, x[m:m + 1].contiguous(), 32)
         assert np.array_equal(y1[0], y4[m]), f"row {m} differs between M=1 and M=4"
-    x32 = synth.make_activation(32, K, seed=78)
-    y32 = _run(4, q, s, b, x32, 32)
-    y8 = _run(4, q, s, b, x32[:8].contiguous(), 32)
-    assert np.array_equal(y8, y32[:8]), "rows differ between M=8 and M=32"
+    x8 = synth.make_activation(8, K, seed=78)
+    y8 = _run(4, q, s, b, x8, 32)
+    y5 = _run(4, q, s, b, x8[:5].contiguous(), 32)
+    assert np.array_equal(y5, y8[:5]), "rows differ between M=5 and M=8"
+
+
+@pytest.mark.parametrize("flags", [0x400, 0x800])
+@pytest.mark.parametrize("bits,M", [(4, 1), (4, 3), (4, 8), (4, 32), (8, 2)])
+def test_every_kernel_family_matches_oracle(port, bits, M, flags):
+    """The shape-agnostic SIMT kernel (0x400) and the register-streaming tensor-core kernel
+    (0x800) are held to the same oracle as the default bulk-copy kernel."""
+    N, K = 528, 2048
+    q, s, b, x = _case(bits, N, K, M, 64, seed=500 + M)
+    want = port.gemv(bits, u32(q), u16(s), u16(b), u16(x), 64)
+    got = _run(bits, q, s, b, x, 64, flags=flags)
+    tol = TOL_EXACT_PATH if (M <= 4 or flags == 0x400) else 1e-2
+    assert_close(got, want, rel_max=tol, what=f"gemv{bits} M={M} flags={flags:#x}")
 
 
 @pytest.mark.parametrize("group", [32, 64])

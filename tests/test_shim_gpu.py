@@ -1,0 +1,70 @@
+"""The C++ operator shim (miori::Metal, miori::Weights, miori::gemv4 ... gemm_mpp32 with the
+reference's signatures) driven like the reference's own test commands, checked against the
+CPU oracle.  Group size is the reference's 32, so oracle/_ref (the reference header itself)
+is the checker when it was built."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from miori_b200 import synth
+from conftest import TOL_EXACT_PATH, assert_close, u16, u32
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+SHIM = os.path.join(HERE, "..", "miori_b200", "libmiori_shim.so")
+
+
+@pytest.fixture(scope="module")
+def shim():
+    lib = C.CDLL(SHIM)
+    lib.miori_shim_last_error.restype = C.c_char_p
+    p, u = C.c_void_p, C.c_uint32
+    lib.miori_shim_test_gemv.argtypes = [C.c_int, p, p, p, p, p, u, u, u]
+    lib.miori_shim_test_prefill.argtypes = [p, p, p, p, p, p, u, u, u]
+    return lib
+
+
+@pytest.mark.parametrize("bits,N,K,B", [(4, 2048, 2048, 1), (4, 512, 2048, 4), (4, 16, 2048, 1),
+                                        (4, 2048, 7680, 2), (8, 4000, 2048, 1), (8, 1024, 2048, 4),
+                                        (4, 1024, 2048, 32)])
+def test_gemv_through_operator_api(shim, port, ref, bits, N, K, B):
+    q, s, b = synth.make_weight(N, K, bits, 32, seed=bits * 1000 + N + B)
+    x = synth.ramp_activation(B, K)  # the reference test's x (src/main.cpp:28)
+    qn, sn, bn, xn = u32(q), u16(s), u16(b), u16(x)
+    y = np.zeros((B, N), np.float32)
+    rc = shim.miori_shim_test_gemv(bits, qn.ctypes.data, sn.ctypes.data, bn.ctypes.data,
+                                   xn.ctypes.data, y.ctypes.data, N, K, B)
+    assert rc == 0, shim.miori_shim_last_error()
+    want = ref.gemv(bits, qn, sn, bn, xn) if ref is not None else port.gemv(bits, qn, sn, bn, xn, 32)
+    assert_close(y, want, rel_max=TOL_EXACT_PATH if B <= 4 else 1e-2, what=f"shim gemv{bits} B={B}")
+    # the reference's own report format (src/main.cpp:80-86)
+    err = np.abs(y - want)
+    print(f"gemv{bits} N={N} K={K} B={B}: max_abs={err.max():.3g} "
+          f"max_rel={(err / (np.abs(want) + 1e-6)).max():.3g}")
+
+
+def test_prefill_through_operator_api(shim, port):
+    """dequant_tile at a cache offset, then gemm_mpp32 and gemm_mpp on 23 rows: both equal the
+    oracle product and each other bit for bit (the reference's test-mpp-tile)."""
+    M, N, K = 23, 6144, 2048
+    q, s, b = synth.make_weight(N, K, 4, 32, seed=77)
+    A = synth.ramp_activation(M, K)
+    qn, sn, bn, An = u32(q), u16(s), u16(b), u16(A)
+    c32, c64 = np.zeros((M, N), np.float32), np.zeros((M, N), np.float32)
+    rc = shim.miori_shim_test_prefill(qn.ctypes.data, sn.ctypes.data, bn.ctypes.data, An.ctypes.data,
+                                      c32.ctypes.data, c64.ctypes.data, M, N, K)
+    assert rc == 0, shim.miori_shim_last_error()
+    assert np.array_equal(c32, c64)
+    want = port.gemm_bf16(An, port.dequant_rowmajor(4, qn, sn, bn, 32))
+    assert_close(c64, want, rel_max=1e-4, what="shim prefill")
+
+
+def test_errors_surface_as_messages(shim):
+    y = np.zeros((1, 16), np.float32)
+    z = np.zeros(4096, np.uint32)
+    # K not a multiple of the group: the operator throws, the entry reports it
+    rc = shim.miori_shim_test_gemv(4, z.ctypes.data, z.ctypes.data, z.ctypes.data, z.ctypes.data,
+                                   y.ctypes.data, 16, 48, 1)
+    assert rc != 0 and b"multiple" in shim.miori_shim_last_error()
