@@ -231,7 +231,7 @@ def main():
     MMAX = max(M_SWEEP)
     x_dev = {M: [synth.make_activation(M, K, seed=50 + M, device=dev) for _, K in SHAPES] for M in M_SWEEP}
     y_loc = {M: [torch.empty((M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
-    y_all = {M: [torch.empty((world, M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
+    y_all = {M: [torch.empty((world * M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
 
     def one_pass(M):
         for projs in stack:
@@ -297,7 +297,7 @@ def main():
     host_x, host_y = {}, {}
     for M in M_SWEEP:
         host_x[M] = [x.cpu().pin_memory() for x in x_dev[M]]
-        host_y[M] = [torch.empty((world, M, N // world)).pin_memory() if world > 1
+        host_y[M] = [torch.empty((world * M, N // world)).pin_memory() if world > 1
                      else torch.empty((M, N)).pin_memory() for N, _ in SHAPES]
         h2d += sum(t.numel() * 2 for t in host_x[M])
         d2h += sum(t.numel() * 4 for t in host_y[M])

@@ -143,6 +143,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // rows are gathered by 2-D tiled TMA at a fixed 1 KiB / gps pitch.
     const bool linear = qlin != nullptr;
     const uint32_t chunks = K / CW, ng = K >> gshift;
+    const bool ktail = linear && chunks < 64u;  // K shorter than one slab of 64 chunks
     const uint32_t qpitch = linear ? K * BITS / 8 : (uint32_t)ROW_BYTES;
     const uint32_t spitch = linear ? ng : gps;
 
@@ -282,23 +283,23 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const uint32_t lc = (i4 * 4u + wg) * 4u + t;  // chunk inside the slab row
                     // past the end of K (linear mode only; tiled TMA zero-fills): a zero scale
                     // and bias against zero-staged x contribute exactly 0
-                    const bool valid = !linear || lc < chunks;
-                    const uint32_t lcc = valid ? lc : 0u;
+                    uint32_t lcc = lc;
+                    bool valid = true;
+                    if (ktail) {  // CTA-uniform: only when K is shorter than one slab
+                        valid = lc < chunks;
+                        lcc = valid ? lc : 0u;
+                    }
                     const uint4 q0 = *reinterpret_cast<const uint4*>(st + g * qpitch + lcc * 16u);
                     const uint4 q1 = *reinterpret_cast<const uint4*>(st + (g + 8u) * qpitch + lcc * 16u);
                     const uint32_t sbi = sbrow + ((lcc * CW) >> gshift);
-                    const uint32_t s0 = valid ? sp[sbi] : 0u, b0 = valid ? bp[sbi] : 0u;
-                    const uint32_t s1 = valid ? sp[sbi + 8u * spitch] : 0u;
-                    const uint32_t b1 = valid ? bp[sbi + 8u * spitch] : 0u;
+                    uint32_t s0 = sp[sbi], b0 = bp[sbi];
+                    uint32_t s1 = sp[sbi + 8u * spitch], b1 = bp[sbi + 8u * spitch];
+                    if (ktail && !valid) s0 = b0 = s1 = b1 = 0u;
                     const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
                     const uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
-                    // two independent accumulation chains (even / odd words)
+                    // two independent accumulation chains (even / odd words), each started by
+                    // an MMA with a zero accumulator input
                     float d0[NT][4], d1[NT][4];
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        d0[j][0] = d0[j][1] = d0[j][2] = d0[j][3] = 0.0f;
-                        d1[j][0] = d1[j][1] = d1[j][2] = d1[j][3] = 0.0f;
-                    }
                     uint32_t s2a = 0, b2a = 0, s2b = 0, b2b = 0;
                     if (!EXACT) {
                         s2a = s0 | (s0 << 16); b2a = b0 | (b0 << 16);
@@ -320,13 +321,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         for (int j = 0; j < NT; ++j) {
                             const uint4 xu = *reinterpret_cast<const uint4*>(
                                 xb[j] + i4 * (4u * STEP_UNITS * 16u) + wd * 16);
-                            if (wd & 1) {
-                                mma_bf16(d1[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
-                                mma_bf16(d1[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
-                            } else {
-                                mma_bf16(d0[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
-                                mma_bf16(d0[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
-                            }
+                            if (wd == 0) mma_bf16_z(d0[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
+                            else if (wd == 1) mma_bf16_z(d1[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
+                            else if (wd & 1) mma_bf16(d1[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
+                            else mma_bf16(d0[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
+                            if (wd & 1) mma_bf16(d1[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
+                            else mma_bf16(d0[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
                         }
                     }
                     if (EXACT) {
@@ -337,11 +337,13 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                         for (int j = 0; j < NT; ++j) {
                             const float xs0 = xsp[(size_t)(2 * j) * cpr + i4 * 16u];
-                            const float xs1 = xsp[(size_t)(2 * j + 1) * cpr + i4 * 16u];
                             acc[j][0] = __fmaf_rn(sc0, d0[j][0] + d1[j][0], __fmaf_rn(bt0, xs0, acc[j][0]));
-                            acc[j][1] = __fmaf_rn(sc0, d0[j][1] + d1[j][1], __fmaf_rn(bt0, xs1, acc[j][1]));
                             acc[j][2] = __fmaf_rn(sc1, d0[j][2] + d1[j][2], __fmaf_rn(bt1, xs0, acc[j][2]));
-                            acc[j][3] = __fmaf_rn(sc1, d0[j][3] + d1[j][3], __fmaf_rn(bt1, xs1, acc[j][3]));
+                            if (2u * j + 1u < M) {  // CTA-uniform: the odd activation row exists
+                                const float xs1 = xsp[(size_t)(2 * j + 1) * cpr + i4 * 16u];
+                                acc[j][1] = __fmaf_rn(sc0, d0[j][1] + d1[j][1], __fmaf_rn(bt0, xs1, acc[j][1]));
+                                acc[j][3] = __fmaf_rn(sc1, d0[j][3] + d1[j][3], __fmaf_rn(bt1, xs1, acc[j][3]));
+                            }
                         }
                     } else {
 #pragma unroll
@@ -435,32 +437,29 @@ size_t fixed_smem(uint32_t K) {
     return bytes;
 }
 
-// Ring plan for this problem: active groups and stages per group; ngrp == 0 means the TMA
-// path cannot take it.
+// Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
+// take the problem.
 struct Plan {
-    uint32_t ngrp, nsg;
+    uint32_t grid, ngrp, nsg;
 };
 template <int BITS, bool EXACT, int NT>
 Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
     constexpr int KC = 16 * 4 * (128 / BITS);
-    Plan p = {0, 0};
+    Plan p = {0, 0, 0};
     if ((K / group) % 8 != 0) return p;  // scale rows must have a 16-byte pitch for TMA
     const size_t fixed = fixed_smem<BITS, EXACT, NT>(K);
     const uint32_t tiles = (N + 15) / 16, kslabs = (K + KC - 1) / KC;
-    const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)sm_count());
-    const uint32_t tiles_cta = (tiles + grid - 1) / grid;  // tiles of the busiest CTA
-    // aim at half an SM so that two consecutive kernels can be resident together; settle for
-    // one CTA per SM when the staged activations are large
-    // one CTA per SM when the staged activations are large, or when the CTA streams many more
-    // slabs than half an SM can hold (a long kernel gains nothing from sharing the SM, and a
-    // saturated HBM needs ~100 KB in flight per SM)
-    const size_t target = 112 * 1024, hard = 208 * 1024;
-    uint32_t st = 0;
-    if (fixed + 4 * STAGE_BYTES <= target) st = (uint32_t)((target - fixed) / STAGE_BYTES);
-    if (st == 0 || tiles_cta * kslabs > 2 * st) {
-        if (fixed + 2 * STAGE_BYTES > hard) return p;
-        st = (uint32_t)((hard - fixed) / STAGE_BYTES);
-    }
+    const uint32_t sms = (uint32_t)sm_count();
+    // A CTA is sized for half an SM (shared memory and, for M <= 2 / 5..8, registers).  Short
+    // kernels launch one CTA per SM so that the next kernel of a dependent-launch chain can be
+    // resident beside it and prefetch; long ones launch two per SM for latency hiding.
+    const size_t half = 112 * 1024, hard = 208 * 1024;
+    const bool fits_half = fixed + 4 * STAGE_BYTES <= half;
+    if (!fits_half && fixed + 2 * STAGE_BYTES > hard) return p;
+    const uint32_t st = (uint32_t)(((fits_half ? half : hard) - fixed) / STAGE_BYTES);
+    const bool two_per_sm = fits_half && NT == 1 && tiles * kslabs > 8 * sms;
+    p.grid = std::min<uint32_t>(tiles, two_per_sm ? 2 * sms : sms);
+    const uint32_t tiles_cta = (tiles + p.grid - 1) / p.grid;  // tiles of the busiest CTA
     p.ngrp = std::min<uint32_t>(std::min<uint32_t>(GROUPS, st), tiles_cta);
     const uint32_t sets = (tiles_cta + p.ngrp - 1) / p.ngrp;
     p.nsg = std::min<uint32_t>(st / p.ngrp, sets * kslabs);  // no more than a group ever needs
@@ -474,8 +473,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
                cudaStream_t stream) {
     constexpr int KC = 16 * 4 * (128 / BITS);
     const size_t smem = fixed_smem<BITS, EXACT, NT>(K) + (size_t)plan.ngrp * plan.nsg * STAGE_BYTES;
-    const uint32_t tiles = (N + 15u) / 16u;
-    const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)sm_count());
+    const uint32_t grid = plan.grid;
     const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
     const uint32_t gshift = group == 32 ? 5u : 6u;
     // K within one slab: plain bulk copies (rows of a tile are contiguous); else tiled TMA
