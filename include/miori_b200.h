@@ -136,6 +136,31 @@ int miori_cache_to_rowmajor(const void* cache, void* out, uint32_t N, uint32_t K
 int miori_gemm_bf16_cache(const void* A, const void* cache, void* C, uint32_t M, uint32_t N,
                           uint32_t K, uint32_t flags, void* stream);
 
+/* Same product with a caller-provided scratch area that lets problems with few output tiles
+ * (small M or N, long K) split K across SMs: partial tiles go to `workspace` (fp32) and a
+ * second kernel sums them in a fixed order, so results stay reproducible and independent of
+ * M.  miori_gemm_workspace_bytes gives the size worth passing (0: the shape does not
+ * split); a smaller or NULL workspace only reduces or disables the splitting.  The workspace
+ * contents are scratch; two launches in flight at once must not share it.  (The reference
+ * has no counterpart: its GEMM is a library call, shaders/gemm_mpp.metal:47-53.) */
+size_t miori_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K);
+int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* C, uint32_t M, uint32_t N,
+                             uint32_t K, uint32_t flags, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* ---- projection dispatch: replaces BatchEngine::linear / linear_p and Engine::p_gemm
+ *      (reference src/batch.cpp:223-230, 429-431, src/engine.cpp:508-518), which route a
+ *      projection to gemv4_b for narrow batches and to the bf16-cache GEMM otherwise. ------ */
+
+/* y[M][N] (fp32) = x[M][K] (bf16) x W^T.  M <= 8 streams the packed 4-bit weights
+ * (miori_gemv4); wider M multiplies the bf16 cache on the tensor cores
+ * (miori_gemm_bf16_cache_ws) when `cache` is given, else stays on the packed weights
+ * (M <= 32).  The reference's cut-over is 4 rows; eight keep fp32-scale or bf16-weight GEMV
+ * bandwidth-bound on this part. */
+int miori_linear4(const void* q, const void* s, const void* b, const void* cache, const void* x,
+                  void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* Non-zero if a kernel of this library recorded an internal error on the current
  * device since the last call (bounded wait expired); clears the record. */
 int miori_device_error_poll(void);

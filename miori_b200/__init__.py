@@ -3,13 +3,23 @@
 The product is libmiori_b200.so (C ABI in include/miori_b200.h) plus the C++ operator shim
 under shim/ that mirrors the reference's src/ops.h.  This package is the thin Python
 binding used by the tests and the benchmark.
-"""
-from . import _lib
-from ._lib import GEMV_EXACT, LAUNCH_PDL, OUT_BF16, OUT_F32, MioriError, lib
-from .ops import (dequant4_cache, dequant4_rowmajor, dequant8_rowmajor, gemm_bf16_cache, gemv4,
-                  gemv8)
 
-__all__ = [
-    "lib", "MioriError", "OUT_F32", "OUT_BF16", "LAUNCH_PDL", "GEMV_EXACT", "gemv4", "gemv8",
-    "dequant4_rowmajor", "dequant8_rowmajor", "dequant4_cache", "gemm_bf16_cache",
-]
+The binding is loaded on first use of any operator or of `lib`; if libmiori_b200.so is
+missing or lacks a declared symbol that access raises -- there is no CPU fallback.
+`miori_b200.build` (the nvcc driver) imports without the library so that it can create it.
+"""
+import importlib
+
+_OPS = ("gemv4", "gemv8", "dequant4_rowmajor", "dequant8_rowmajor", "dequant4_cache",
+        "cache_to_rowmajor", "gemm_bf16_cache", "gemm_workspace", "linear4")
+_LIB = ("lib", "check", "MioriError", "OUT_F32", "OUT_BF16", "LAUNCH_PDL", "GEMV_EXACT")
+
+__all__ = list(_OPS + _LIB)
+
+
+def __getattr__(name):
+    if name in _OPS:
+        return getattr(importlib.import_module(".ops", __name__), name)
+    if name in _LIB:
+        return getattr(importlib.import_module("._lib", __name__), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

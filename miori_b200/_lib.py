@@ -45,6 +45,9 @@ _SIGS = {
     "miori_dequant4_cache": (_i, [_p, _p, _p, _p, _u32, _u32, _u32, _p]),
     "miori_cache_to_rowmajor": (_i, [_p, _p, _u32, _u32, _p]),
     "miori_gemm_bf16_cache": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
+    "miori_gemm_workspace_bytes": (_sz, [_u32, _u32, _u32]),
+    "miori_gemm_bf16_cache_ws": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p, _sz, _p]),
+    "miori_linear4": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p, _sz, _p]),
     "miori_device_error_poll": (_i, []),
 }
 

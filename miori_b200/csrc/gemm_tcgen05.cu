@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "tma_host.cuh"
 
+#include <algorithm>
+
 namespace miori_b200 {
 namespace gemm {
 
@@ -103,7 +105,8 @@ template <int BN, bool OUT_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cout,
-                         uint32_t M, uint32_t N, uint32_t K) {
+                         float* __restrict__ ws, uint32_t splits, uint32_t M, uint32_t N,
+                         uint32_t K) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
@@ -119,7 +122,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
-    const uint32_t tiles = m_blocks * n_blocks;
+    // split-K: work item t covers k-blocks [kb0, kb1) of output tile t / splits and writes its
+    // fp32 partial to slice t % splits of the workspace (splits == 1: straight to C)
+    const uint32_t tiles = m_blocks * n_blocks * splits;
     const uint32_t k_blocks = K / BK;
 
     pdl_launch_dependents();
@@ -156,8 +161,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t it = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
-                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
+                const uint32_t sp = t % splits;
+                const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
+                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 1))) break;
                     mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
@@ -178,7 +185,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!(ok = mbar_wait(tempty_bar(acc), aph ^ 1u, &abort_flag, 2))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+                const uint32_t sp = t % splits;
+                const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
+                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
                     if (!(ok = mbar_wait(full_bar(s), ph, &abort_flag, 3))) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -188,7 +197,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                     for (uint32_t k = 0; k < BK / UMMA_K; ++k) {
                         // advance 32 bytes (16 bf16) inside the swizzled 128-byte row
-                        umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0u);
+                        umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0) || (k != 0u));
                     }
                     umma_commit(empty_bar(s));  // slot reusable once these MMAs have read it
                 }
@@ -200,7 +209,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t tile_it = 0;
         bool ok = true;
         for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
-            const TileCoord tc = tile_coord(t, m_blocks, n_blocks);
+            const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
+            float* part = ws + (size_t)(t % splits) * M * N;  // used when splits > 1
             const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
             ok = mbar_wait(tfull_bar(acc), aph, &abort_flag, 4);
             ok = __all_sync(0xFFFFFFFFu, ok);
@@ -214,7 +224,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < M) {
-                    if (OUT_BF16) {
+                    if (OUT_BF16 && splits == 1u) {
                         uint16_t* dst = reinterpret_cast<uint16_t*>(Cout) + (size_t)row * N + col0 + c;
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -232,7 +242,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                         }
                     } else {
-                        float* dst = reinterpret_cast<float*>(Cout) + (size_t)row * N + col0 + c;
+                        float* dst = (splits == 1u ? reinterpret_cast<float*>(Cout) : part) +
+                                     (size_t)row * N + col0 + c;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             if (col0 + c + 4u * j < N)
@@ -264,6 +275,43 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
+// Sum the split-K partials in slice order (deterministic) and write C as fp32 or bf16.
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float4* __restrict__ ws, void* __restrict__ Cout, size_t quads,
+                     uint32_t splits) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads;
+         i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = ws[i];
+        for (uint32_t s = 1; s < splits; ++s) {
+            const float4 b = ws[(size_t)s * quads + i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (OUT_BF16) {
+            uint2 o;
+            o.x = float_to_bf16_bits(a.x) | (float_to_bf16_bits(a.y) << 16);
+            o.y = float_to_bf16_bits(a.z) | (float_to_bf16_bits(a.w) << 16);
+            reinterpret_cast<uint2*>(Cout)[i] = o;
+        } else {
+            reinterpret_cast<float4*>(Cout)[i] = a;
+        }
+    }
+}
+
+// Number of K splits worth using: only when the output tiles alone would leave most SMs
+// idle, never fewer than 4 k-blocks per split, at most 16.
+static uint32_t choose_splits(uint32_t tiles, uint32_t k_blocks, size_t ws_bytes, size_t mn) {
+    const uint32_t sms = (uint32_t)sm_count();
+    if (tiles * 4 > sms * 3 || k_blocks < 8) return 1;
+    uint32_t s = (sms + tiles - 1) / tiles;
+    s = std::min<uint32_t>(s, k_blocks / 4);
+    s = std::min<uint32_t>(s, 16);
+    if (mn) s = (uint32_t)std::min<size_t>(s, ws_bytes / (mn * 4));
+    return s < 2 ? 1 : s;
+}
+
 // [rows][K] bf16 row-major, box = [box_rows][64], 128-byte swizzle, zero fill out of range.
 static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
                      uint32_t box_rows) {
@@ -273,14 +321,14 @@ static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 
 template <int BN>
 static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N, uint32_t K,
-                       uint32_t flags, cudaStream_t stream) {
+                       uint32_t flags, float* ws, uint32_t splits, cudaStream_t stream) {
     using C = Cfg<BN>;
     CUtensorMap ta, tb;
     int rc = make_tmap(&ta, A, M, K, BM);
     if (rc) return rc;
     rc = make_tmap(&tb, Bc, N, K, BN);
     if (rc) return rc;
-    const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     uint32_t grid = (uint32_t)sm_count();
     if (grid > tiles) grid = tiles;
     const bool bf16 = (flags & MIORI_OUT_BF16) != 0, pdl = (flags & MIORI_LAUNCH_PDL) != 0;
@@ -290,16 +338,56 @@ static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e == cudaSuccess)
             e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
-                       Cm, M, N, K);
+                       Cm, ws, splits, M, N, K);
     } else {
         auto kern = gemm_bf16_tcgen05_kernel<BN, false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e == cudaSuccess)
             e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
-                       Cm, M, N, K);
+                       Cm, ws, splits, M, N, K);
     }
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05 launch");
+    if (splits > 1) {
+        const size_t quads = (size_t)M * N / 4;
+        const unsigned blocks = (unsigned)std::min<size_t>((quads + 255) / 256, (size_t)sm_count() * 8);
+        if (bf16)
+            e = launch(splitk_reduce_kernel<true>, dim3(blocks), dim3(256), 0, stream, pdl,
+                       reinterpret_cast<const float4*>(ws), Cm, quads, splits);
+        else
+            e = launch(splitk_reduce_kernel<false>, dim3(blocks), dim3(256), 0, stream, pdl,
+                       reinterpret_cast<const float4*>(ws), Cm, quads, splits);
+        if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce launch");
+    }
     return MIORI_OK;
+}
+
+// Shape checks shared by the GEMM entries.
+static int check_gemm_args(const char* op, const void* A, const void* cache, const void* Cm,
+                           uint32_t M, uint32_t N, uint32_t K) {
+    if (!A || !cache || !Cm) return fail(MIORI_E_INVALID, "%s: null pointer", op);
+    if (M == 0 || N == 0 || K == 0)
+        return fail(MIORI_E_INVALID, "%s: empty shape M=%u N=%u K=%u", op, M, N, K);
+    if (K % 64 != 0) return fail(MIORI_E_INVALID, "%s: K=%u is not a multiple of 64", op, K);
+    if (N % 8 != 0) return fail(MIORI_E_INVALID, "%s: N=%u is not a multiple of 8", op, N);
+    if (!aligned16(A) || !aligned16(cache) || !aligned16(Cm))
+        return fail(MIORI_E_INVALID, "%s: A, cache and C must be 16-byte aligned", op);
+    return MIORI_OK;
+}
+
+// Tile shape and split count for a problem (workspace of ws_bytes available, 0 = none).
+struct GemmPlan {
+    bool wide;
+    uint32_t splits;
+};
+static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, size_t ws_bytes) {
+    const uint32_t m_blocks = (M + BM - 1) / BM;
+    const uint32_t tiles256 = m_blocks * ((N + 255) / 256);
+    GemmPlan p;
+    // Wide tiles amortise B traffic; narrow ones fill the SMs when there are few tiles.
+    p.wide = (tiles256 >= (uint32_t)sm_count() && !(flags & 0x100u)) || (flags & 0x200u);
+    const uint32_t tiles = p.wide ? tiles256 : m_blocks * ((N + 127) / 128);
+    p.splits = ws_bytes ? choose_splits(tiles, K / BK, ws_bytes, (size_t)M * N) : 1;
+    return p;
 }
 
 }  // namespace gemm
@@ -307,22 +395,27 @@ static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint
 
 using namespace miori_b200;
 
+MIORI_API int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* Cm, uint32_t M,
+                                       uint32_t N, uint32_t K, uint32_t flags, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+    int rc = gemm::check_gemm_args("miori_gemm_bf16_cache", A, cache, Cm, M, N, K);
+    if (rc) return rc;
+    if (workspace && !aligned16(workspace))
+        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: workspace must be 16-byte aligned");
+    const gemm::GemmPlan p = gemm::plan_gemm(M, N, K, flags, workspace ? workspace_bytes : 0);
+    float* ws = reinterpret_cast<float*>(workspace);
+    if (p.wide)
+        return gemm::launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, p.splits, (cudaStream_t)stream);
+    return gemm::launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, p.splits, (cudaStream_t)stream);
+}
+
 MIORI_API int miori_gemm_bf16_cache(const void* A, const void* cache, void* Cm, uint32_t M,
                                     uint32_t N, uint32_t K, uint32_t flags, void* stream) {
-    if (!A || !cache || !Cm) return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: null pointer");
-    if (M == 0 || N == 0 || K == 0)
-        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: empty shape M=%u N=%u K=%u", M, N, K);
-    if (K % 64 != 0)
-        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: K=%u is not a multiple of 64", K);
-    if (N % 8 != 0)
-        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: N=%u is not a multiple of 8", N);
-    if (!aligned16(A) || !aligned16(cache) || !aligned16(Cm))
-        return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: A, cache and C must be 16-byte aligned");
-    // Wide tiles amortise B traffic; narrow ones fill the SMs when there are few tiles.
-    const uint32_t m_blocks = (M + gemm::BM - 1) / gemm::BM;
-    const uint32_t tiles256 = m_blocks * ((N + 255) / 256);
-    const bool wide = tiles256 >= (uint32_t)sm_count() && !(flags & 0x100u);
-    if (wide || (flags & 0x200u))
-        return gemm::launch_gemm<256>(A, cache, Cm, M, N, K, flags, (cudaStream_t)stream);
-    return gemm::launch_gemm<128>(A, cache, Cm, M, N, K, flags, (cudaStream_t)stream);
+    return miori_gemm_bf16_cache_ws(A, cache, Cm, M, N, K, flags, nullptr, 0, stream);
+}
+
+MIORI_API size_t miori_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K) {
+    if (M == 0 || N == 0 || K < 64) return 0;
+    const gemm::GemmPlan p = gemm::plan_gemm(M, N, K, 0, (size_t)16 * M * N * 4);
+    return p.splits > 1 ? (size_t)p.splits * M * N * 4 : 0;
 }

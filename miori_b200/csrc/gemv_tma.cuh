@@ -158,6 +158,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     float* red = xsum + (EXACT ? (size_t)MP * cpr : 0);                  // [GROUPS] group areas
 
     pdl_launch_dependents();
+    if (threadIdx.x == 0) timeline_mark(N, 0);  // CTA started
 
     // This CTA's tiles.  Slabs are enumerated in sets of ngrp tiles (one
     // per active group), k-slab major inside a set, so that consecutive slabs belong to
@@ -220,12 +221,15 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         try_refill();  // fills the rings: up to nstage slabs in flight before the wait
     }
 
+    if (threadIdx.x == 0) timeline_mark(N, 1);  // ring filled, about to wait
     pdl_wait_prior();  // x (and y) belong to the predecessor until here
+    if (threadIdx.x == 0) timeline_mark(N, 2);  // predecessor complete
 
     stage_x_padded<BITS, EXACT, MP>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
+    if (threadIdx.x == 0) timeline_mark(N, 3);  // x staged
 
     // per-lane constants: byte offsets inside a stage and inside the staged x
     const uint32_t n = lane >> 2;
@@ -274,6 +278,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 ok = mbar_wait(smem_addr(&full_bars[stage]), parity, &abort_flag, 0x10);
                 ok = __all_sync(0xFFFFFFFFu, ok);
             }
+            if (threadIdx.x == 0) timeline_mark(N, 4);  // slab arrived
             if (ok && !dbg_skip) {
                 const uint8_t* st = ring + (size_t)stage * STAGE_BYTES;
                 const uint16_t* sp = reinterpret_cast<const uint16_t*>(st + Q_BYTES);
@@ -397,6 +402,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 mine[(g + 8) * MP + 8 * j + 2 * t + 1] = acc[j][3];
             }
         }
+        if (threadIdx.x == 0) timeline_mark(N, 5);  // math done
         named_barrier(1u + grp, 128u);
         const uint32_t gt = wg * 32u + lane;  // thread index inside the group
 #pragma unroll
@@ -418,6 +424,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         ++tile_it;
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+        if (threadIdx.x == 0) timeline_mark(N, 6);  // tile stored
     }
 
     if (abort_flag) {  // let copies still in flight land before the CTA's memory is released

@@ -60,6 +60,15 @@ MIORI_API int miori_gemv8(const void* q, const void* s, const void* b, const voi
     return gemv_entry<8>("miori_gemv8", q, s, b, x, y, N, K, M, group, flags, stream);
 }
 
+MIORI_API int miori_linear4(const void* q, const void* s, const void* b, const void* cache,
+                            const void* x, void* y, uint32_t N, uint32_t K, uint32_t M,
+                            uint32_t group, uint32_t flags, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+    if (M <= 8 || !cache)
+        return miori_gemv4(q, s, b, x, y, N, K, M, group, flags, stream);
+    return miori_gemm_bf16_cache_ws(x, cache, y, M, N, K, flags, workspace, workspace_bytes, stream);
+}
+
 MIORI_API int miori_dequant4_rowmajor(const void* q, const void* s, const void* b, void* out,
                                       uint32_t N, uint32_t K, uint32_t group, void* stream) {
     int rc = check_quant_args("miori_dequant4_rowmajor", q, s, b, N, K, group);
@@ -96,6 +105,17 @@ MIORI_API int miori_cache_to_rowmajor(const void* cache, void* out, uint32_t N, 
     if (!cache || !out) return fail(MIORI_E_INVALID, "miori_cache_to_rowmajor: null pointer");
     MIORI_CUDA(cudaMemcpyAsync(out, cache, (size_t)N * K * 2, cudaMemcpyDeviceToDevice,
                                (cudaStream_t)stream));
+    return MIORI_OK;
+}
+
+// Profiling aid (not declared in the public header): install a device buffer of `cap` records
+// (2 x u64 each) that instrumented kernels append timestamps to; buf == NULL switches it off.
+MIORI_API int miori_debug_timeline(void* buf, unsigned int cap) {
+    unsigned long long* p = reinterpret_cast<unsigned long long*>(buf);
+    const unsigned int zero = 0;
+    MIORI_CUDA(cudaMemcpyToSymbol(g_timeline, &p, sizeof(p)));
+    MIORI_CUDA(cudaMemcpyToSymbol(g_timeline_cap, &cap, sizeof(cap)));
+    MIORI_CUDA(cudaMemcpyToSymbol(g_timeline_pos, &zero, sizeof(zero)));
     return MIORI_OK;
 }
 

@@ -78,12 +78,35 @@ def cache_to_rowmajor(cache, N, K):
     return o
 
 
-def gemm_bf16_cache(A, cache, N, flags=0, out=None):
-    """C[M][N] = A[M][K] x cache(N,K)^T on the tcgen05 tensor cores."""
+def gemm_workspace(M, N, K, device):
+    """Scratch tensor of the size miori_gemm_workspace_bytes recommends, or None."""
+    nbytes = lib.miori_gemm_workspace_bytes(M, N, K)
+    return torch.empty(nbytes // 4, dtype=torch.float32, device=device) if nbytes else None
+
+
+def gemm_bf16_cache(A, cache, N, flags=0, out=None, workspace=None):
+    """C[M][N] = A[M][K] x cache(N,K)^T on the tcgen05 tensor cores (split-K if a workspace
+    tensor is given and the shape has few output tiles)."""
     _need_cuda(A, cache)
     M, K = A.shape
     dt = torch.bfloat16 if flags & OUT_BF16 else torch.float32
     Cm = out if out is not None else torch.empty((M, N), dtype=dt, device=A.device)
-    check(lib.miori_gemm_bf16_cache(A.data_ptr(), cache.data_ptr(), Cm.data_ptr(), M, N, K, flags,
-                                    _stream()))
+    wp = workspace.data_ptr() if workspace is not None else None
+    wb = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    check(lib.miori_gemm_bf16_cache_ws(A.data_ptr(), cache.data_ptr(), Cm.data_ptr(), M, N, K, flags,
+                                       wp, wb, _stream()))
     return Cm
+
+
+def linear4(q, s, b, cache, x, group=32, flags=0, out=None, workspace=None):
+    """Projection dispatch (packed-weight GEMV for M <= 8, bf16-cache GEMM above)."""
+    _need_cuda(q, s, b, x)
+    M, K = x.shape
+    N = q.shape[0]
+    y = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    wp = workspace.data_ptr() if workspace is not None else None
+    wb = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    check(lib.miori_linear4(q.data_ptr(), s.data_ptr(), b.data_ptr(),
+                            cache.data_ptr() if cache is not None else None, x.data_ptr(),
+                            y.data_ptr(), N, K, M, group, flags, wp, wb, _stream()))
+    return y

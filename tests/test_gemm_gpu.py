@@ -99,3 +99,45 @@ def test_linearity_at_full_size():
     assert torch.equal(miori_b200.gemm_bf16_cache(A, cache, N), c1)
     ref = A[:64].float() @ ops.cache_to_rowmajor(cache, N, K).float().T  # torch fp32 spot check
     assert torch.allclose(c1[:64], ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(32, 2048, 2048), (16, 3072, 2048), (32, 2048, 8192), (9, 512, 1024),
+                                   (200, 256, 4096)])
+def test_split_k_with_workspace_matches_oracle(port, M, N, K):
+    """Few output tiles: K is split across SMs through a caller-provided workspace and summed
+    in a fixed order."""
+    q, s, b, cache = _weights(N, K, 64, seed=M * 3 + N + K)
+    A = synth.make_activation(M, K, seed=21, device=DEV)
+    ws = miori_b200.gemm_workspace(M, N, K, DEV)
+    assert ws is not None, "expected this shape to split"
+    c_split = miori_b200.gemm_bf16_cache(A, cache, N, workspace=ws)
+    c_plain = miori_b200.gemm_bf16_cache(A, cache, N)
+    torch.cuda.synchronize()
+    want = port.gemm_bf16(u16(A), port.dequant_rowmajor(4, u32(q), u16(s), u16(b), 64))
+    assert_close(c_split.cpu().numpy(), want, rel_max=1e-4, what=f"split-K {M}x{N}x{K}")
+    assert_close(c_plain.cpu().numpy(), want, rel_max=1e-4, what=f"plain {M}x{N}x{K}")
+    # reproducible, independent of M, bf16 epilogue is the rounded fp32 result
+    assert torch.equal(miori_b200.gemm_bf16_cache(A, cache, N, workspace=ws), c_split)
+    half = miori_b200.gemm_bf16_cache(A[:M // 2 + 1].contiguous(), cache, N, workspace=ws)
+    assert torch.equal(half, c_split[:M // 2 + 1])
+    c16 = miori_b200.gemm_bf16_cache(A, cache, N, flags=miori_b200.OUT_BF16, workspace=ws)
+    assert torch.equal(c16, c_split.to(torch.bfloat16))
+    assert miori_b200.lib.miori_device_error_poll() == 0
+
+
+@pytest.mark.parametrize("M", [1, 4, 8, 9, 32])
+def test_linear_dispatch(port, M):
+    """miori_linear4 routes M <= 8 to the packed-weight GEMV and wider M to the cache GEMM
+    (the reference's BatchEngine::linear policy, src/batch.cpp:223-230)."""
+    N, K = 3072, 2048
+    q, s, b, cache = _weights(N, K, 64, seed=31)
+    x = synth.make_activation(M, K, seed=32, device=DEV)
+    ws = miori_b200.gemm_workspace(max(M, 9), N, K, DEV)
+    y = miori_b200.linear4(q, s, b, cache, x, group=64, workspace=ws)
+    y_nocache = miori_b200.linear4(q, s, b, None, x, group=64)
+    torch.cuda.synchronize()
+    want = port.gemv(4, u32(q), u16(s), u16(b), u16(x), 64)
+    assert_close(y.cpu().numpy(), want, what=f"linear4 M={M}")
+    assert_close(y_nocache.cpu().numpy(), want, what=f"linear4 (no cache) M={M}")
+    if M <= 8:
+        assert torch.equal(y, miori_b200.gemv4(q, s, b, x, group=64))
