@@ -148,6 +148,23 @@ int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* C, uint32_t
                              uint32_t K, uint32_t flags, void* workspace, size_t workspace_bytes,
                              void* stream);
 
+/* The split-K GEMM for callers that cannot supply a workspace because they cannot allocate
+ * device memory when they call: e.g. a decode loop that divided up the GPU's memory once at
+ * start-up, or a plug-in in a process where another runtime owns the allocator.  (No
+ * counterpart in the reference, whose GEMM is a closed library call.)  The K-split partials go
+ * to a 16 MiB array built into the library (miori_gemm_static_scratch_bytes); every GPU that
+ * loads the library holds that array until the process exits.  The call allocates nothing --
+ * no cudaMalloc / cudaFree, no allocating library routine.  Shapes whose preferred split needs
+ * more than the array are refused with MIORI_E_INVALID and a message that names the sizes;
+ * shapes that do not split at all run without touching it.  The first call on a device looks
+ * up the array's device address, so make that call before starting any stream capture.  All
+ * calls share the one array: it keeps whatever the last call left (nothing needs clearing,
+ * every partial is overwritten before it is read), and two calls whose kernels overlap on the
+ * GPU -- different streams, or different host threads -- race on it; keep them in one stream. */
+size_t miori_gemm_static_scratch_bytes(void);
+int miori_gemm_bf16_cache_static(const void* A, const void* cache, void* C, uint32_t M, uint32_t N,
+                                 uint32_t K, uint32_t flags, void* stream);
+
 /* ---- projection dispatch: replaces BatchEngine::linear / linear_p and Engine::p_gemm
  *      (reference src/batch.cpp:223-230, 429-431, src/engine.cpp:508-518), which route a
  *      projection to gemv4_b for narrow batches and to the bf16-cache GEMM otherwise. ------ */

@@ -47,6 +47,8 @@ _SIGS = {
     "miori_gemm_bf16_cache": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
     "miori_gemm_workspace_bytes": (_sz, [_u32, _u32, _u32]),
     "miori_gemm_bf16_cache_ws": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p, _sz, _p]),
+    "miori_gemm_static_scratch_bytes": (_sz, []),
+    "miori_gemm_bf16_cache_static": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
     "miori_linear4": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p, _sz, _p]),
     "miori_device_error_poll": (_i, []),
 }

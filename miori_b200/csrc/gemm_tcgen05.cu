@@ -19,6 +19,7 @@
 #include "tma_host.cuh"
 
 #include <algorithm>
+#include <mutex>
 
 namespace miori_b200 {
 namespace gemm {
@@ -412,6 +413,60 @@ MIORI_API int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* C
 MIORI_API int miori_gemm_bf16_cache(const void* A, const void* cache, void* Cm, uint32_t M,
                                     uint32_t N, uint32_t K, uint32_t flags, void* stream) {
     return miori_gemm_bf16_cache_ws(A, cache, Cm, M, N, K, flags, nullptr, 0, stream);
+}
+
+// ---- split-K GEMM on built-in scratch ------------------------------------------------------
+// Some hosts cannot hand this library a workspace because they cannot allocate device memory
+// at the point of the call: a decode loop whose device memory was carved up once at start-up,
+// or a plug-in living in a process where another runtime owns the allocator.  For them the
+// split-K partials go to this fixed array, which every GPU that loads the library carries
+// until the process exits.  Host code must not pass the array's name to a kernel (on the host
+// the name is only a stand-in); its device address is looked up once per device below.
+constexpr size_t kStaticScratchBytes = (size_t)16 << 20;  // 16 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+// Device address of g_static_scratch on the current device (looked up on first use there).
+static int static_scratch_ptr(float** out) {
+    static float* ptrs[64];
+    static std::mutex mu;
+    int dev = 0;
+    MIORI_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MIORI_E_INVALID, "device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        ptrs[dev] = static_cast<float*>(p);
+    }
+    *out = ptrs[dev];
+    return MIORI_OK;
+}
+
+MIORI_API size_t miori_gemm_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+MIORI_API int miori_gemm_bf16_cache_static(const void* A, const void* cache, void* Cm, uint32_t M,
+                                           uint32_t N, uint32_t K, uint32_t flags, void* stream) {
+    int rc = gemm::check_gemm_args("miori_gemm_bf16_cache_static", A, cache, Cm, M, N, K);
+    if (rc) return rc;
+    // the split count the shape wants with unlimited scratch decides whether it fits
+    const gemm::GemmPlan want = gemm::plan_gemm(M, N, K, flags, ~(size_t)0 >> 1);
+    const size_t need = want.splits > 1 ? (size_t)want.splits * M * N * sizeof(float) : 0;
+    if (need > kStaticScratchBytes)
+        return fail(MIORI_E_INVALID,
+                    "miori_gemm_bf16_cache_static: M=%u N=%u K=%u needs %zu bytes of scratch (%u "
+                    "K-splits), the built-in scratch holds %zu; use miori_gemm_bf16_cache_ws",
+                    M, N, K, need, want.splits, kStaticScratchBytes);
+    float* ws = nullptr;
+    if (want.splits > 1) {
+        rc = static_scratch_ptr(&ws);
+        if (rc) return rc;
+    }
+    // every element of every partial slice is written by the GEMM before the reduction reads
+    // it, so the previous call's contents never need clearing
+    if (want.wide)
+        return gemm::launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, want.splits, (cudaStream_t)stream);
+    return gemm::launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, want.splits, (cudaStream_t)stream);
 }
 
 MIORI_API size_t miori_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K) {
