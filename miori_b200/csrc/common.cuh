@@ -52,25 +52,7 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 // word 0: error count, word 1: code of the first failure, word 2/3: detail.
 __device__ unsigned int g_device_error[4];
 
-// Optional timeline probe (off unless miori_debug_timeline() installs a buffer): block 0 of
-// an instrumented kernel appends {kernel tag, point, globaltimer ns} records.
-__device__ unsigned long long* g_timeline;
-__device__ unsigned int g_timeline_pos;
-__device__ unsigned int g_timeline_cap;
-
 #ifdef __CUDACC__
-__device__ __forceinline__ void timeline_mark(unsigned tag, unsigned point) {
-    unsigned long long* buf = g_timeline;
-    if (buf == nullptr || blockIdx.x != 0) return;
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const unsigned i = atomicAdd(&g_timeline_pos, 1u);
-    if (i < g_timeline_cap) {
-        buf[2 * i] = ((unsigned long long)tag << 32) | point;
-        buf[2 * i + 1] = t;
-    }
-}
-
 __device__ __forceinline__ void device_error(unsigned code, unsigned d0, unsigned d1) {
     if (atomicAdd(&g_device_error[0], 1u) == 0u) {
         g_device_error[1] = code;

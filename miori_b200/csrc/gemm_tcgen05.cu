@@ -102,6 +102,41 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t m_blocks, u
     return c;
 }
 
+// Store 32 consecutive accumulator columns of one row: fp32 to C (or to the split-K partial
+// slice), or bf16 to C; columns at or past N are masked in groups of 4 / 8 (N % 8 == 0).
+template <bool OUT_BF16>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], uint32_t row, uint32_t M,
+                                            uint32_t N, uint32_t col, void* Cout, float* part,
+                                            uint32_t splits) {
+    if (row >= M) return;
+    if (OUT_BF16 && splits == 1u) {
+        uint16_t* dst = reinterpret_cast<uint16_t*>(Cout) + (size_t)row * N + col;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (col + 8u * j < N) {
+                uint4 v;
+                v.x = float_to_bf16_bits(__uint_as_float(r[8 * j + 0])) |
+                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 1])) << 16);
+                v.y = float_to_bf16_bits(__uint_as_float(r[8 * j + 2])) |
+                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 3])) << 16);
+                v.z = float_to_bf16_bits(__uint_as_float(r[8 * j + 4])) |
+                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 5])) << 16);
+                v.w = float_to_bf16_bits(__uint_as_float(r[8 * j + 6])) |
+                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 7])) << 16);
+                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+            }
+        }
+    } else {
+        float* dst = (splits == 1u ? reinterpret_cast<float*>(Cout) : part) + (size_t)row * N + col;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (col + 4u * j < N)
+                *reinterpret_cast<uint4*>(dst + 4 * j) =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+    }
+}
+
 template <int BN, bool OUT_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -224,35 +259,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < M) {
-                    if (OUT_BF16 && splits == 1u) {
-                        uint16_t* dst = reinterpret_cast<uint16_t*>(Cout) + (size_t)row * N + col0 + c;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (col0 + c + 8u * j < N) {
-                                uint4 v;
-                                v.x = float_to_bf16_bits(__uint_as_float(r[8 * j + 0])) |
-                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 1])) << 16);
-                                v.y = float_to_bf16_bits(__uint_as_float(r[8 * j + 2])) |
-                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 3])) << 16);
-                                v.z = float_to_bf16_bits(__uint_as_float(r[8 * j + 4])) |
-                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 5])) << 16);
-                                v.w = float_to_bf16_bits(__uint_as_float(r[8 * j + 6])) |
-                                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 7])) << 16);
-                                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
-                            }
-                        }
-                    } else {
-                        float* dst = (splits == 1u ? reinterpret_cast<float*>(Cout) : part) +
-                                     (size_t)row * N + col0 + c;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (col0 + c + 4u * j < N)
-                                *reinterpret_cast<uint4*>(dst + 4 * j) =
-                                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                        }
-                    }
-                }
+                store_chunk<OUT_BF16>(r, row, M, N, col0 + c, Cout, part, splits);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -275,6 +282,224 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      : "memory");
     }
 }
+
+// ---------------------------------------------------------------------------------------
+// Two-CTA variant: a cluster of two CTAs (one SM pair) computes a 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  CTA r of the pair owns rows [128r, 128r+128) of the tile (its A
+// tile and its TMEM accumulator) and loads only rows [128r, 128r+128) of the B tile; the MMA,
+// issued by CTA 0, reads both halves of B out of the two CTAs' shared memory.  Per k-block
+// every SM therefore pulls 32 KB through L2 for a 128 x 256 x 64 block of work instead of
+// 48 KB, which is what keeps the tensor pipe fed.  TMA loads of both CTAs complete on CTA 0's
+// "full" barrier (no multicast is involved); CTA 0 releases stages and publishes
+// accumulators to both CTAs with tcgen05.commit ... multicast::cluster.
+namespace pair {
+
+constexpr int BN = 256;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;         // 16 KB: this CTA's 128 rows of A
+constexpr int B_BYTES = (BN / 2) * BK * 2;   // 16 KB: this CTA's 128 rows of B
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 2 * BN;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
+                 ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on the same barrier offset in both CTAs of the pair once the MMAs issued so far finish
+__device__ __forceinline__ void umma_commit_both(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;"
+        ::"r"(bar), "h"(mask)
+        : "memory");
+}
+// arrive on a barrier of CTA 0 from either CTA of the pair
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar_local) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, 0;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(bar_local)
+        : "memory");
+}
+
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                              const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cout,
+                              float* __restrict__ ws, uint32_t splits, uint32_t M, uint32_t N,
+                              uint32_t K) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t raw = smem_addr(smem_raw);
+    const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+    const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rank = cluster_ctarank();           // 0 = leader of the pair
+    const uint32_t pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t m_blocks = (M + 2 * BM - 1) / (2 * BM), n_blocks = (N + BN - 1) / BN;
+    const uint32_t tiles = m_blocks * n_blocks * splits;
+    const uint32_t k_blocks = K / BK;
+
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0u;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);    // leader's copy is the one in use: one expect_tx arrival
+            mbar_init(empty_bar(s), 1);   // one multicast commit from the leader
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);   // one multicast commit from the leader
+            mbar_init(tempty_bar(a), 8);  // leader's copy: four epilogue warps of each CTA
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_addr(&tmem_base_slot)), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();  // both CTAs' barriers exist before any remote arrive or multicast commit
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    pdl_wait_prior();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // producer of this CTA: its A rows and its half of the B rows, both completing on
+            // the leader's full barrier
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t t = pair_id; t < tiles && ok; t += pairs) {
+                const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
+                const uint32_t sp = t % splits;
+                const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
+                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 0x21))) break;
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2u * STAGE_BYTES);
+                    const uint32_t sa = tiles_base + s * STAGE_BYTES;
+                    const uint32_t fb = full_bar(s) & PEER_MASK;
+                    tma_load_2d_pair(sa, &tmap_a, (int)(kb * BK),
+                                     (int)(tc.m_blk * 2 * BM + rank * BM), fb);
+                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, (int)(kb * BK),
+                                     (int)(tc.n_blk * BN + rank * (BN / 2)), fb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // the pair's single MMA issuer
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (uint32_t t = pair_id; t < tiles && ok; t += pairs, ++tile_it) {
+                const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+                if (!(ok = mbar_wait(tempty_bar(acc), aph ^ 1u, &abort_flag, 0x22))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t sp = t % splits;
+                const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
+                for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!(ok = mbar_wait(full_bar(s), ph, &abort_flag, 0x23))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = tiles_base + s * STAGE_BYTES;
+                    const uint64_t adesc = umma_desc_sw128(sa);
+                    const uint64_t bdesc = umma_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                    for (uint32_t k = 0; k < BK / UMMA_K; ++k)
+                        umma_f16_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                      (kb > kb0) || (k != 0u));
+                    umma_commit_both(empty_bar(s));
+                }
+                if (ok) umma_commit_both(tfull_bar(acc));
+            }
+        }
+    } else {
+        const uint32_t quad = warp & 3u;
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (uint32_t t = pair_id; t < tiles && ok; t += pairs, ++tile_it) {
+            const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
+            float* part = ws + (size_t)(t % splits) * M * N;
+            const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+            ok = mbar_wait(tfull_bar(acc), aph, &abort_flag, 0x24);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t row = tc.m_blk * 2 * BM + rank * BM + quad * 32u + lane;
+            const uint32_t col0 = tc.n_blk * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < (uint32_t)BN; c += 32u) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                store_chunk<OUT_BF16>(r, row, M, N, col0 + c, Cout, part, splits);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
+        }
+    }
+
+    __syncwarp();
+    if (abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();  // the peer may still signal this CTA's barriers or read its shared memory
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+}  // namespace pair
 
 // Sum the split-K partials in slice order (deterministic) and write C as fp32 or bf16.
 template <bool OUT_BF16>
@@ -301,11 +526,12 @@ splitk_reduce_kernel(const float4* __restrict__ ws, void* __restrict__ Cout, siz
     }
 }
 
-// Number of K splits worth using: only when the output tiles alone would leave most SMs
-// idle, never fewer than 4 k-blocks per split, at most 16.
+// Number of K splits worth using: only when the output tiles alone would leave most SMs idle
+// (the partials cost a second kernel and 8 bytes of traffic per output element per split),
+// never fewer than 4 k-blocks per split, at most 16.
 static uint32_t choose_splits(uint32_t tiles, uint32_t k_blocks, size_t ws_bytes, size_t mn) {
     const uint32_t sms = (uint32_t)sm_count();
-    if (tiles * 4 > sms * 3 || k_blocks < 8) return 1;
+    if (tiles * 3 > sms || k_blocks < 8) return 1;  // only when under a third of the SMs have a tile
     uint32_t s = (sms + tiles - 1) / tiles;
     s = std::min<uint32_t>(s, k_blocks / 4);
     s = std::min<uint32_t>(s, 16);
@@ -318,6 +544,64 @@ static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
                      uint32_t box_rows) {
     return make_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, rows, BK, box_rows,
                         CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// Launch the two-CTA kernel: clusters of 2, one pair per SM pair.
+static int launch_gemm_pair(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N,
+                            uint32_t K, uint32_t flags, float* ws, uint32_t splits,
+                            cudaStream_t stream) {
+    CUtensorMap ta, tb;
+    int rc = make_tmap(&ta, A, M, K, BM);
+    if (rc) return rc;
+    rc = make_tmap(&tb, Bc, N, K, pair::BN / 2);
+    if (rc) return rc;
+    const uint32_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + pair::BN - 1) / pair::BN) * splits;
+    uint32_t pairs = (uint32_t)sm_count() / 2;
+    if (pairs > tiles) pairs = tiles;
+    const bool bf16 = (flags & MIORI_OUT_BF16) != 0, pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
+    cudaError_t e;
+    if (bf16) {
+        auto kern = pair::gemm_bf16_tcgen05_pair_kernel<true>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cm, ws, splits, M, N, K);
+    } else {
+        auto kern = pair::gemm_bf16_tcgen05_pair_kernel<false>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cm, ws, splits, M, N, K);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05_pair launch");
+    return MIORI_OK;
+}
+
+// Fixed-order reduction of split-K partials into C.
+static int launch_reduce(void* Cm, uint32_t M, uint32_t N, uint32_t flags, float* ws, uint32_t splits,
+                         cudaStream_t stream) {
+    const bool bf16 = (flags & MIORI_OUT_BF16) != 0, pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    const size_t quads = (size_t)M * N / 4;
+    const unsigned blocks = (unsigned)std::min<size_t>((quads + 255) / 256, (size_t)sm_count() * 8);
+    cudaError_t e;
+    if (bf16)
+        e = launch(splitk_reduce_kernel<true>, dim3(blocks), dim3(256), 0, stream, pdl,
+                   reinterpret_cast<const float4*>(ws), Cm, quads, splits);
+    else
+        e = launch(splitk_reduce_kernel<false>, dim3(blocks), dim3(256), 0, stream, pdl,
+                   reinterpret_cast<const float4*>(ws), Cm, quads, splits);
+    if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce launch");
+    return MIORI_OK;
 }
 
 template <int BN>
@@ -348,17 +632,7 @@ static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint
                        Cm, ws, splits, M, N, K);
     }
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05 launch");
-    if (splits > 1) {
-        const size_t quads = (size_t)M * N / 4;
-        const unsigned blocks = (unsigned)std::min<size_t>((quads + 255) / 256, (size_t)sm_count() * 8);
-        if (bf16)
-            e = launch(splitk_reduce_kernel<true>, dim3(blocks), dim3(256), 0, stream, pdl,
-                       reinterpret_cast<const float4*>(ws), Cm, quads, splits);
-        else
-            e = launch(splitk_reduce_kernel<false>, dim3(blocks), dim3(256), 0, stream, pdl,
-                       reinterpret_cast<const float4*>(ws), Cm, quads, splits);
-        if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce launch");
-    }
+    if (splits > 1) return launch_reduce(Cm, M, N, flags, ws, splits, stream);
     return MIORI_OK;
 }
 
@@ -377,7 +651,8 @@ static int check_gemm_args(const char* op, const void* A, const void* cache, con
 
 // Tile shape and split count for a problem (workspace of ws_bytes available, 0 = none).
 struct GemmPlan {
-    bool wide;
+    bool wide;   // 128 x 256 tiles instead of 128 x 128 (single-CTA kernel)
+    bool pair;   // 256 x 256 tiles on SM pairs (two-CTA kernel)
     uint32_t splits;
 };
 static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, size_t ws_bytes) {
@@ -386,9 +661,25 @@ static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, si
     GemmPlan p;
     // Wide tiles amortise B traffic; narrow ones fill the SMs when there are few tiles.
     p.wide = (tiles256 >= (uint32_t)sm_count() && !(flags & 0x100u)) || (flags & 0x200u);
-    const uint32_t tiles = p.wide ? tiles256 : m_blocks * ((N + 127) / 128);
+    // SM pairs when there are enough 256 x 256 tiles to occupy them (tuning flags: 0x4000
+    // forces the pair kernel, 0x8000 forbids it)
+    const uint32_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
+    p.pair = ((tiles_pair * 2 >= (uint32_t)sm_count() / 2 && M > 128 && !(flags & 0x300u)) ||
+              (flags & 0x4000u)) && !(flags & 0x8000u);
+    const uint32_t tiles = p.pair ? 2 * tiles_pair : (p.wide ? tiles256 : m_blocks * ((N + 127) / 128));
     p.splits = ws_bytes ? choose_splits(tiles, K / BK, ws_bytes, (size_t)M * N) : 1;
     return p;
+}
+
+static int run_plan(const GemmPlan& p, const void* A, const void* cache, void* Cm, uint32_t M,
+                    uint32_t N, uint32_t K, uint32_t flags, float* ws, cudaStream_t stream) {
+    if (p.pair) {
+        int rc = launch_gemm_pair(A, cache, Cm, M, N, K, flags, ws, p.splits, stream);
+        if (rc == MIORI_OK && p.splits > 1) rc = launch_reduce(Cm, M, N, flags, ws, p.splits, stream);
+        return rc;
+    }
+    if (p.wide) return launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, p.splits, stream);
+    return launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, p.splits, stream);
 }
 
 }  // namespace gemm
@@ -405,9 +696,7 @@ MIORI_API int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* C
         return fail(MIORI_E_INVALID, "miori_gemm_bf16_cache: workspace must be 16-byte aligned");
     const gemm::GemmPlan p = gemm::plan_gemm(M, N, K, flags, workspace ? workspace_bytes : 0);
     float* ws = reinterpret_cast<float*>(workspace);
-    if (p.wide)
-        return gemm::launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, p.splits, (cudaStream_t)stream);
-    return gemm::launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, p.splits, (cudaStream_t)stream);
+    return gemm::run_plan(p, A, cache, Cm, M, N, K, flags, ws, (cudaStream_t)stream);
 }
 
 MIORI_API int miori_gemm_bf16_cache(const void* A, const void* cache, void* Cm, uint32_t M,
@@ -464,9 +753,7 @@ MIORI_API int miori_gemm_bf16_cache_static(const void* A, const void* cache, voi
     }
     // every element of every partial slice is written by the GEMM before the reduction reads
     // it, so the previous call's contents never need clearing
-    if (want.wide)
-        return gemm::launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, want.splits, (cudaStream_t)stream);
-    return gemm::launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, want.splits, (cudaStream_t)stream);
+    return gemm::run_plan(want, A, cache, Cm, M, N, K, flags, ws, (cudaStream_t)stream);
 }
 
 MIORI_API size_t miori_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K) {

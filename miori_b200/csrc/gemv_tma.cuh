@@ -119,7 +119,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_b, const uint8_t* __restrict__ qlin,
                 const uint16_t* __restrict__ slin, const uint16_t* __restrict__ blin,
                 const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
-                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t dbg_skip) {
+                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar,
+                uint32_t dbg_skip) {
     using namespace gemvmma;
     const uint32_t nstage = ngrp * nsg;  // every active group owns a private ring of nsg stages
     constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
@@ -156,9 +157,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     uint4* zeros = xs + (size_t)MP * pitch;                              // ZERO_BYTES of zeros
     float* xsum = reinterpret_cast<float*>(zeros + ZERO_BYTES / 16);     // [MP][cpr] (EXACT)
     float* red = xsum + (EXACT ? (size_t)MP * cpr : 0);                  // [GROUPS] group areas
+    float* kred = red + (size_t)GROUPS * Red<MP>::GROUP_FLOATS;          // [2][GROUPS][16*MP]
 
     pdl_launch_dependents();
-    if (threadIdx.x == 0) timeline_mark(N, 0);  // CTA started
 
     // This CTA's tiles.  Slabs are enumerated in sets of ngrp tiles (one
     // per active group), k-slab major inside a set, so that consecutive slabs belong to
@@ -166,8 +167,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // ever waited on by one group, in order, so barrier parities are never ambiguous.
     // tiles are dealt round-robin (tile = blockIdx.x + j*gridDim.x): at any moment the CTAs
     // stream one contiguous window of the weight matrix, which HBM serves best
-    const uint32_t ntiles = (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
-    const uint32_t total = ntiles * kslabs;
+    // When a CTA has fewer tiles than groups and K spans several slabs, kpar groups share a
+    // tile: each takes every kpar-th k-slab (a "virtual tile") and their partial outputs are
+    // summed in a fixed order at the end.  kslabs is a multiple of kpar.
+    const uint32_t ntiles = ((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) * kpar;  // virtual
+    const uint32_t kslabs_v = kslabs / kpar;
+    const uint32_t total = ntiles * kslabs_v;
         const uint32_t stage_tx = Q_BYTES + 2u * 16u * gps * 2u;  // bytes tiled TMA delivers per slab
 
     // producer side (lane 0 of the producer warp only)
@@ -186,7 +191,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             const uint32_t bar = smem_addr(&full_bars[stage]);
             const uint32_t dst = smem_addr(ring + (size_t)stage * STAGE_BYTES);
-            const uint32_t row = (blockIdx.x + (p_set0 + p_gi) * gridDim.x) * 16u;
+            const uint32_t vt = p_set0 + p_gi;
+            const uint32_t row = (blockIdx.x + (vt / kpar) * gridDim.x) * 16u;
+            const uint32_t ks = vt % kpar + p_ks * kpar;
             if (linear) {
                 const uint32_t nrows = min(16u, N - row);  // rows past N keep stale (unused) data
                 mbar_expect_tx(bar, nrows * (qpitch + 4u * spitch));
@@ -195,9 +202,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 bulk_g2s(dst + Q_BYTES + SB_BYTES, blin + (size_t)row * spitch, nrows * spitch * 2u, bar);
             } else {
                 mbar_expect_tx(bar, stage_tx);
-                tma_load_2d(dst, &tmap_q, (int)(p_ks * (ROW_BYTES / 4)), (int)row, bar);
-                tma_load_2d(dst + Q_BYTES, &tmap_s, (int)(p_ks * gps), (int)row, bar);
-                tma_load_2d(dst + Q_BYTES + SB_BYTES, &tmap_b, (int)(p_ks * gps), (int)row, bar);
+                tma_load_2d(dst, &tmap_q, (int)(ks * (ROW_BYTES / 4)), (int)row, bar);
+                tma_load_2d(dst + Q_BYTES, &tmap_s, (int)(ks * gps), (int)row, bar);
+                tma_load_2d(dst + Q_BYTES + SB_BYTES, &tmap_b, (int)(ks * gps), (int)row, bar);
             }
             ++issued;
             // advance the cursor: next group of the set, then next k-slab, then next set
@@ -205,7 +212,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (++p_gi == nt) {
                 p_gi = 0;
                 if (++p_kmod == nsg) { p_kmod = 0; ++p_use; }
-                if (++p_ks == kslabs) { p_ks = 0; p_set0 += ngrp; }
+                if (++p_ks == kslabs_v) { p_ks = 0; p_set0 += ngrp; }
             }
         }
     };
@@ -221,15 +228,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         try_refill();  // fills the rings: up to nstage slabs in flight before the wait
     }
 
-    if (threadIdx.x == 0) timeline_mark(N, 1);  // ring filled, about to wait
     pdl_wait_prior();  // x (and y) belong to the predecessor until here
-    if (threadIdx.x == 0) timeline_mark(N, 2);  // predecessor complete
 
     stage_x_padded<BITS, EXACT, MP>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
-    if (threadIdx.x == 0) timeline_mark(N, 3);  // x staged
 
     // per-lane constants: byte offsets inside a stage and inside the staged x
     const uint32_t n = lane >> 2;
@@ -270,15 +274,19 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (uint32_t set0 = 0; warp < WARPS && set0 < ntiles; set0 += ngrp) {
         const uint32_t nt = min(ngrp, ntiles - set0);
         if (grp >= nt) break;
-        const uint32_t tile = blockIdx.x + (set0 + grp) * gridDim.x;
-        for (uint32_t ks = 0; ks < kslabs; ++ks) {
+        const uint32_t vt = set0 + grp, kp = vt % kpar;
+        const uint32_t tile = blockIdx.x + (vt / kpar) * gridDim.x;
+        // start at this group's first k-slab of the row
+#pragma unroll
+        for (int j = 0; j < NT; ++j) xb[j] += (size_t)kp * xadv[j];
+        xsp += (size_t)kp * 64;
+        for (uint32_t ks = 0; ks < kslabs_v; ++ks) {
             const uint32_t stage = grp * nsg + c_kmod, parity = c_par;
             if (++c_kmod == nsg) { c_kmod = 0; c_par ^= 1u; }
             if (ok) {
                 ok = mbar_wait(smem_addr(&full_bars[stage]), parity, &abort_flag, 0x10);
                 ok = __all_sync(0xFFFFFFFFu, ok);
             }
-            if (threadIdx.x == 0) timeline_mark(N, 4);  // slab arrived
             if (ok && !dbg_skip) {
                 const uint8_t* st = ring + (size_t)stage * STAGE_BYTES;
                 const uint16_t* sp = reinterpret_cast<const uint16_t*>(st + Q_BYTES);
@@ -363,12 +371,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (lane == 0) mbar_arrive(smem_addr(&empty_bars[stage]));  // stage consumed
             }
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xb[j] += xadv[j];
-            xsp += 64;
+            for (int j = 0; j < NT; ++j) xb[j] += (size_t)kpar * xadv[j];
+            xsp += (size_t)kpar * 64;
         }
 #pragma unroll
-        for (int j = 0; j < NT; ++j) xb[j] -= (size_t)kslabs * xadv[j];
-        xsp -= (size_t)kslabs * 64;
+        for (int j = 0; j < NT; ++j) xb[j] -= (size_t)(kslabs + kp) * xadv[j];
+        xsp -= (size_t)(kslabs + kp) * 64;
 
         // ---- tile complete: quad sum (EXACT), then 4 partials per output through shared memory
         constexpr int WS = Red<MP>::WS;
@@ -402,7 +410,6 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 mine[(g + 8) * MP + 8 * j + 2 * t + 1] = acc[j][3];
             }
         }
-        if (threadIdx.x == 0) timeline_mark(N, 5);  // math done
         named_barrier(1u + grp, 128u);
         const uint32_t gt = wg * 32u + lane;  // thread index inside the group
 #pragma unroll
@@ -414,17 +421,36 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
             const uint32_t row = tile * 16u + r;
-            if (w == 0 && m < M && row < N && ok) {
+            if (kpar > 1u) {
+                if (w == 0) kred[((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP) + o] = v;
+            } else if (w == 0 && m < M && row < N && ok) {
                 if (OUT_BF16)
                     reinterpret_cast<uint16_t*>(y)[(size_t)m * N + row] = (uint16_t)float_to_bf16_bits(v);
                 else
                     reinterpret_cast<float*>(y)[(size_t)m * N + row] = v;
             }
         }
+        if (kpar > 1u) {
+            // the kpar groups of this tile meet; the first of them sums the partials in order
+            named_barrier(5u + grp / kpar, kpar * 128u);
+            if (kp == 0u) {
+                const float* kr = kred + ((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP);
+                for (uint32_t o = gt; o < 16u * MP; o += 128u) {
+                    float v = kr[o];
+                    for (uint32_t j = 1; j < kpar; ++j) v += kr[(size_t)j * (16 * MP) + o];
+                    const uint32_t r = o & 15u, m = o >> 4, row = tile * 16u + r;
+                    if (m < M && row < N && ok) {
+                        if (OUT_BF16)
+                            reinterpret_cast<uint16_t*>(y)[(size_t)m * N + row] = (uint16_t)float_to_bf16_bits(v);
+                        else
+                            reinterpret_cast<float*>(y)[(size_t)m * N + row] = v;
+                    }
+                }
+            }
+        }
         ++tile_it;
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-        if (threadIdx.x == 0) timeline_mark(N, 6);  // tile stored
     }
 
     if (abort_flag) {  // let copies still in flight land before the CTA's memory is released
@@ -441,18 +467,19 @@ size_t fixed_smem(uint32_t K) {
     size_t bytes = (size_t)MP * (steps_p * STEP_UNITS + 1) * 16 + ZERO_BYTES;
     if (EXACT) bytes += (size_t)MP * steps_p * 4 * 4;
     bytes += (size_t)GROUPS * Red<MP>::GROUP_FLOATS * 4;
+    bytes += (size_t)2 * GROUPS * 16 * MP * 4;  // partial outputs of groups that share a tile
     return bytes;
 }
 
 // Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
 // take the problem.
 struct Plan {
-    uint32_t grid, ngrp, nsg;
+    uint32_t grid, ngrp, nsg, kpar;
 };
 template <int BITS, bool EXACT, int NT>
 Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
     constexpr int KC = 16 * 4 * (128 / BITS);
-    Plan p = {0, 0, 0};
+    Plan p = {0, 0, 0, 1};
     if ((K / group) % 8 != 0) return p;  // scale rows must have a 16-byte pitch for TMA
     const size_t fixed = fixed_smem<BITS, EXACT, NT>(K);
     const uint32_t tiles = (N + 15) / 16, kslabs = (K + KC - 1) / KC;
@@ -467,9 +494,16 @@ Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
     const bool two_per_sm = fits_half && NT == 1 && tiles * kslabs > 8 * sms;
     p.grid = std::min<uint32_t>(tiles, two_per_sm ? 2 * sms : sms);
     const uint32_t tiles_cta = (tiles + p.grid - 1) / p.grid;  // tiles of the busiest CTA
-    p.ngrp = std::min<uint32_t>(std::min<uint32_t>(GROUPS, st), tiles_cta);
-    const uint32_t sets = (tiles_cta + p.ngrp - 1) / p.ngrp;
-    p.nsg = std::min<uint32_t>(st / p.ngrp, sets * kslabs);  // no more than a group ever needs
+    // few tiles per CTA and a long K: let 2 or 4 groups share a tile, each taking every
+    // kpar-th k-slab
+    while (p.kpar * 2 <= (uint32_t)GROUPS && tiles_cta * p.kpar * 2 <= (uint32_t)GROUPS &&
+           kslabs % (p.kpar * 2) == 0 && st >= p.kpar * 2)
+        p.kpar *= 2;
+    const uint32_t vtiles = tiles_cta * p.kpar;
+    p.ngrp = std::min<uint32_t>(std::min<uint32_t>(GROUPS, st), vtiles);
+    p.ngrp -= p.ngrp % p.kpar;
+    const uint32_t sets = (vtiles + p.ngrp - 1) / p.ngrp;
+    p.nsg = std::min<uint32_t>(st / p.ngrp, sets * (kslabs / p.kpar));  // no more than a group needs
     if (p.ngrp * p.nsg > (uint32_t)MAX_STAGES) p.nsg = MAX_STAGES / p.ngrp;
     return p;
 }
@@ -506,7 +540,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
         if (e == cudaSuccess)                                                                    \
             e = launch(kern, dim3(grid), dim3(THREADS), smem, stream, pdl, tq, ts, tb, ql,       \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
-                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg,  \
+                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
                        (flags & 0x1000u) ? 1u : 0u);        \
     } while (0)
     if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true); else MIORI_TMA_LAUNCH(false);

@@ -108,17 +108,6 @@ MIORI_API int miori_cache_to_rowmajor(const void* cache, void* out, uint32_t N, 
     return MIORI_OK;
 }
 
-// Profiling aid (not declared in the public header): install a device buffer of `cap` records
-// (2 x u64 each) that instrumented kernels append timestamps to; buf == NULL switches it off.
-MIORI_API int miori_debug_timeline(void* buf, unsigned int cap) {
-    unsigned long long* p = reinterpret_cast<unsigned long long*>(buf);
-    const unsigned int zero = 0;
-    MIORI_CUDA(cudaMemcpyToSymbol(g_timeline, &p, sizeof(p)));
-    MIORI_CUDA(cudaMemcpyToSymbol(g_timeline_cap, &cap, sizeof(cap)));
-    MIORI_CUDA(cudaMemcpyToSymbol(g_timeline_pos, &zero, sizeof(zero)));
-    return MIORI_OK;
-}
-
 MIORI_API int miori_device_error_poll(void) {
     unsigned int rec[4] = {0, 0, 0, 0};
     if (cudaMemcpyFromSymbol(rec, g_device_error, sizeof(rec)) != cudaSuccess) return 0;

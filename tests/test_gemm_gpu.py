@@ -14,7 +14,7 @@ from conftest import assert_close, u16, u32
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-WIDE, NARROW = 0x200, 0x100  # tile-shape overrides of miori_gemm_bf16_cache (tuning flags)
+WIDE, NARROW, PAIR, NOPAIR = 0x200, 0x100, 0x4000, 0x8000  # kernel-shape overrides (tuning flags)
 
 
 def _weights(N, K, group, seed):
@@ -23,7 +23,7 @@ def _weights(N, K, group, seed):
     return q, s, b, cache
 
 
-@pytest.mark.parametrize("flags", [0, WIDE, NARROW])
+@pytest.mark.parametrize("flags", [0, WIDE, NARROW, PAIR])
 @pytest.mark.parametrize("M,N,K", [(192, 512, 2048), (64, 256, 64), (1, 8, 64), (128, 128, 128),
                                    (300, 1000, 448), (33, 16, 2048), (257, 6144, 512)])
 def test_gemm_matches_oracle(port, M, N, K, flags):
@@ -68,8 +68,10 @@ def test_rows_do_not_depend_on_m_tiling():
     c23 = miori_b200.gemm_bf16_cache(A[:23].contiguous(), cache, N)
     c64 = miori_b200.gemm_bf16_cache(A, cache, N)
     c23w = miori_b200.gemm_bf16_cache(A[:23].contiguous(), cache, N, flags=WIDE)
+    c64p = miori_b200.gemm_bf16_cache(A, cache, N, flags=PAIR)
     assert torch.equal(c23, c64[:23])
     assert torch.equal(c23, c23w)
+    assert torch.equal(c64p, c64)
 
 
 def test_bf16_output_and_guard_bands():
