@@ -175,7 +175,7 @@ def run_reference_arm(args):
 def workload_config(args, world):
     return {"workload": "decode_stack_int4: 24 layers x {2048->3072, 2048->2048, 2048->16384, "
                         "8192->2048}, M in {1,2,4,8,16,32}", "group": args.group, "bits": 4,
-            "layers": LAYERS, "m_sweep": M_SWEEP, "out": "f32",
+            "layers": args.layers, "m_sweep": M_SWEEP, "out": "f32",
             "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
             "l2": "inputs larger than L2 (821 MB of weights per pass)"}
 
@@ -192,6 +192,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="stack depth (24 is the benchmark)")
+    ap.add_argument("--verbose", action="store_true", help="progress on stderr")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -206,6 +208,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    layers = args.layers
+
+    def say(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     torch.cuda.set_device(local)
@@ -217,7 +225,7 @@ def main():
 
     # ---- weights: every rank holds its row shard of every projection
     stack = []
-    for l in range(LAYERS):
+    for l in range(layers):
         projs = []
         for i, (N, K) in enumerate(SHAPES):
             assert N % (16 * world) == 0
@@ -227,7 +235,8 @@ def main():
             projs.append((q[sl].contiguous(), s[sl].contiguous(), b[sl].contiguous()))
             del q, s, b
         stack.append(projs)
-    bytes_pass = LAYERS * sum(packed_bytes(N, K, 4, G) for N, K in SHAPES)  # whole job
+    bytes_pass = layers * sum(packed_bytes(N, K, 4, G) for N, K in SHAPES)  # whole job
+    say("weights ready")
     MMAX = max(M_SWEEP)
     x_dev = {M: [synth.make_activation(M, K, seed=50 + M, device=dev) for _, K in SHAPES] for M in M_SWEEP}
     y_loc = {M: [torch.empty((M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
@@ -250,13 +259,15 @@ def main():
     for M in M_SWEEP:
         one_pass(M)
     torch.cuda.synchronize()
+    say("eager passes done")
     graphs = {}
     for M in M_SWEEP:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             one_pass(M)
         graphs[M] = g
-    launches_pass = LAYERS * len(SHAPES)
+    launches_pass = layers * len(SHAPES)
+    say("graphs captured")
 
     def step():
         for M in M_SWEEP:
@@ -290,6 +301,7 @@ def main():
     ms_total = timed(step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
+    say(f"timed region done: {ms_step:.3f} ms/step")
     value = len(M_SWEEP) * bytes_pass / (ms_step * 1e-3) / 1e9
 
     # ---- per-M breakdown (each M timed alone, same graphs)
@@ -321,6 +333,7 @@ def main():
                 check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
             check(lib.miori_stream_sync(stream))  # the host consumes this pass's result
 
+    say("per-M breakdown done")
     e2e_step()
     ms_e2e = timed(e2e_step, args.steps) / args.steps
     e2e_val = len(M_SWEEP) * bytes_pass / (ms_e2e * 1e-3) / 1e9
@@ -356,9 +369,15 @@ def main():
         out["cpu_baseline"] = cpu_decode_sample(G, seconds=12.0)
         out["cpu_baseline"].pop("seconds", None)
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Captured graphs hold NCCL work and tearing the communicator down under them can block;
+        # every rank has finished the same work here, so leave without the teardown.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def extras(torch, miori_b200, synth, dev, G, peaks, timed):
