@@ -192,6 +192,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--eager", action="store_true",
+                    help="launch the passes directly instead of replaying CUDA graphs (for a "
+                         "profiler's launch list; timings then include host launch overhead)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="stack depth (24 is the benchmark)")
     ap.add_argument("--verbose", action="store_true", help="progress on stderr")
     args = ap.parse_args()
@@ -260,8 +263,18 @@ def main():
         one_pass(M)
     torch.cuda.synchronize()
     say("eager passes done")
+    class Eager:
+        def __init__(self, M):
+            self.M = M
+
+        def replay(self):
+            one_pass(self.M)
+
     graphs = {}
     for M in M_SWEEP:
+        if args.eager:
+            graphs[M] = Eager(M)
+            continue
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             one_pass(M)
@@ -311,6 +324,33 @@ def main():
         per_m[str(M)] = {"ms_per_pass": ms, "gbs": bytes_pass / (ms * 1e-3) / 1e9,
                          "us_per_launch": 1e3 * ms / launches_pass,
                          "path": "gemv4 on packed int4" if M <= 8 else "tcgen05 GEMM on the bf16 cache"}
+
+    # ---- the same M=1 pass with the four projections of a layer on four concurrent streams
+    # (no dependency between them): separates kernel throughput from launch-chain latency
+    if world == 1 and not args.eager:
+        side = [torch.cuda.Stream(device=dev) for _ in SHAPES]
+        y_ind = [torch.empty((1, N), device=dev) for N, _ in SHAPES]
+
+        def independent_pass():
+            cur = torch.cuda.current_stream()
+            for st in side:
+                st.wait_stream(cur)
+            for projs in stack:
+                for (q, s, b), x, y, st in zip(projs, x_dev[1], y_ind, side):
+                    with torch.cuda.stream(st):
+                        miori_b200.gemv4(q, s, b, x, group=G, flags=pdl, out=y)
+            for st in side:
+                cur.wait_stream(st)
+        independent_pass()
+        torch.cuda.synchronize()
+        gi = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gi):
+            independent_pass()
+        ms = timed(gi.replay, max(3, args.steps // 2)) / max(3, args.steps // 2)
+        per_m["1"]["four_streams_gbs"] = bytes_pass / (ms * 1e-3) / 1e9
+        per_m["1"]["four_streams_note"] = ("same 96 launches, each projection type on its own stream: "
+                                           "four independent PDL chains run concurrently")
+        say("independent-stream pass done")
 
     # ---- e2e: host buffers through the C ABI, copies inside the timed region
     stream = torch.cuda.current_stream().cuda_stream
