@@ -246,8 +246,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const bool active = EXACT ? ((n >> 1) == t) : true;
         xb[j] = active ? reinterpret_cast<const uint8_t*>(xs + (size_t)m * pitch + x_unit(wg, t, 0))
                        : reinterpret_cast<const uint8_t*>(zeros);
-        xadv[j] = active ? (uint32_t)SLAB_X_BYTES : 0u;
+        xadv[j] = active ? (uint32_t)SLAB_X_BYTES * kpar : 0u;  // groups sharing a tile stride kpar slabs
     }
+    const uint32_t xs_adv = 64u * kpar;  // chunk sums per k-slab stride
     const float* xsp = xsum + wg * 4u + t;  // chunk (ks*16 + i4*4 + wg)*4 + t of row 0
     float* gred = red + (size_t)grp * Red<MP>::GROUP_FLOATS;
 
@@ -277,9 +278,11 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t vt = set0 + grp, kp = vt % kpar;
         const uint32_t tile = blockIdx.x + (vt / kpar) * gridDim.x;
         // start at this group's first k-slab of the row
+        if (kpar > 1u) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j) xb[j] += (size_t)kp * xadv[j];
-        xsp += (size_t)kp * 64;
+            for (int j = 0; j < NT; ++j) xb[j] += kp * (xadv[j] / kpar);
+            xsp += kp * 64u;
+        }
         for (uint32_t ks = 0; ks < kslabs_v; ++ks) {
             const uint32_t stage = grp * nsg + c_kmod, parity = c_par;
             if (++c_kmod == nsg) { c_kmod = 0; c_par ^= 1u; }
@@ -371,12 +374,13 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (lane == 0) mbar_arrive(smem_addr(&empty_bars[stage]));  // stage consumed
             }
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xb[j] += (size_t)kpar * xadv[j];
-            xsp += (size_t)kpar * 64;
+            for (int j = 0; j < NT; ++j) xb[j] += xadv[j];
+            xsp += xs_adv;
         }
+        // back to k-slab 0 of the row
 #pragma unroll
-        for (int j = 0; j < NT; ++j) xb[j] -= (size_t)(kslabs + kp) * xadv[j];
-        xsp -= (size_t)(kslabs + kp) * 64;
+        for (int j = 0; j < NT; ++j) xb[j] -= kslabs_v * xadv[j] + (kpar > 1u ? kp * (xadv[j] / kpar) : 0u);
+        xsp -= kslabs_v * xs_adv + (kpar > 1u ? kp * 64u : 0u);
 
         // ---- tile complete: quad sum (EXACT), then 4 partials per output through shared memory
         constexpr int WS = Red<MP>::WS;
