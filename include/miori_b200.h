@@ -44,6 +44,15 @@ extern "C" {
                                   must be immutable while in flight) and waits for the
                                   predecessor before touching x / A or writing y / C */
 #define MIORI_GEMV_EXACT 4u    /* force the fp32-dequant GEMV path for every M (default: M<=4) */
+/* Kernel-selection overrides, for tests and A/B timing only.  Every choice computes the same
+ * result; the default heuristics pick among them by shape. */
+#define MIORI_TUNE_GEMM_NARROW 0x100u  /* GEMM: 128x128 tiles */
+#define MIORI_TUNE_GEMM_WIDE 0x200u    /* GEMM: 128x256 tiles, one CTA per tile */
+#define MIORI_TUNE_GEMV_SIMT 0x400u    /* GEMV: the scalar-FMA kernel */
+#define MIORI_TUNE_GEMV_LDG 0x800u     /* GEMV: tensor-core kernel fed by plain loads (no TMA) */
+#define MIORI_TUNE_GEMV_TILED 0x2000u  /* GEMV: tiled TMA even where linear bulk copies fit */
+#define MIORI_TUNE_GEMM_PAIR 0x4000u   /* GEMM: two-CTA (cta_group::2) kernel */
+#define MIORI_TUNE_GEMM_NOPAIR 0x8000u /* GEMM: never the two-CTA kernel */
 
 const char* miori_last_error(void);
 /* Library version string, e.g. "miori_b200 0.1 sm_100a". */

@@ -10,7 +10,8 @@ import os
 import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmiori_b200.so")
+# MIORI_B200_LIB points at another build of the library (A/B comparisons of kernels)
+LIB_PATH = os.environ.get("MIORI_B200_LIB") or os.path.join(HERE, "libmiori_b200.so")
 HEADER = os.path.join(HERE, "..", "include", "miori_b200.h")
 
 OUT_F32, OUT_BF16, LAUNCH_PDL, GEMV_EXACT = 0, 1, 2, 4

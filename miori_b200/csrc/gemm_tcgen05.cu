@@ -660,12 +660,12 @@ static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, si
     const uint32_t tiles256 = m_blocks * ((N + 255) / 256);
     GemmPlan p;
     // Wide tiles amortise B traffic; narrow ones fill the SMs when there are few tiles.
-    p.wide = (tiles256 >= (uint32_t)sm_count() && !(flags & 0x100u)) || (flags & 0x200u);
+    p.wide = (tiles256 >= (uint32_t)sm_count() && !(flags & MIORI_TUNE_GEMM_NARROW)) || (flags & MIORI_TUNE_GEMM_WIDE);
     // SM pairs when there are enough 256 x 256 tiles to occupy them (tuning flags: 0x4000
     // forces the pair kernel, 0x8000 forbids it)
     const uint32_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
     p.pair = ((tiles_pair * 2 >= (uint32_t)sm_count() / 2 && M > 128 && !(flags & 0x300u)) ||
-              (flags & 0x4000u)) && !(flags & 0x8000u);
+              (flags & MIORI_TUNE_GEMM_PAIR)) && !(flags & MIORI_TUNE_GEMM_NOPAIR);
     const uint32_t tiles = p.pair ? 2 * tiles_pair : (p.wide ? tiles256 : m_blocks * ((N + 127) / 128));
     p.splits = ws_bytes ? choose_splits(tiles, K / BK, ws_bytes, (size_t)M * N) : 1;
     return p;

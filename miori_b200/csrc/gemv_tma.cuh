@@ -54,6 +54,25 @@ __device__ __forceinline__ uint32_t shr_mulhi(uint32_t w, int k) {
     return r;
 }
 
+// Shared-memory loads by 32-bit shared address (one instruction each, no generic addressing).
+// volatile: the data arrives through TMA, so the loads must stay behind the mbarrier wait.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float ldsf32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -119,8 +138,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_b, const uint8_t* __restrict__ qlin,
                 const uint16_t* __restrict__ slin, const uint16_t* __restrict__ blin,
                 const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
-                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar,
-                uint32_t dbg_skip) {
+                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar) {
     using namespace gemvmma;
     const uint32_t nstage = ngrp * nsg;  // every active group owns a private ring of nsg stages
     constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
@@ -235,21 +253,26 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
 
-    // per-lane constants: byte offsets inside a stage and inside the staged x
+    // per-lane constants, all as 32-bit shared addresses / byte offsets
     const uint32_t n = lane >> 2;
-    const uint32_t sbrow = g * spitch;                            // bf16 index of row g's groups
-    const uint8_t* xb[NT];  // B-fragment base of this lane: k-slab 0, step wg
+    const uint32_t lc0 = wg * 4u + t;                               // first chunk of this lane in a slab
+    const uint32_t ring_a = smem_addr(ring);
+    const uint32_t q_lane = g * qpitch + lc0 * 16u;                 // + i4*256 per step, + 8*qpitch for row g+8
+    const uint32_t sb_lane = Q_BYTES + (g * spitch + ((lc0 * CW) >> gshift)) * 2u;
+    const uint32_t sb_step = ((16u * CW) >> gshift) * 2u;           // groups advance per step (bytes)
+    const uint32_t sb_row8 = 8u * spitch * 2u;
+    uint32_t xb[NT];        // B-fragment base of this lane: k-slab 0, step wg
     uint32_t xadv[NT];      // advance per k-slab (0 for masked lanes, which read zeros)
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const uint32_t m = EXACT ? (2u * j + (n & 1u)) : (8u * j + n);
         const bool active = EXACT ? ((n >> 1) == t) : true;
-        xb[j] = active ? reinterpret_cast<const uint8_t*>(xs + (size_t)m * pitch + x_unit(wg, t, 0))
-                       : reinterpret_cast<const uint8_t*>(zeros);
+        xb[j] = active ? smem_addr(xs + (size_t)m * pitch + x_unit(wg, t, 0)) : smem_addr(zeros);
         xadv[j] = active ? (uint32_t)SLAB_X_BYTES * kpar : 0u;  // groups sharing a tile stride kpar slabs
     }
-    const uint32_t xs_adv = 64u * kpar;  // chunk sums per k-slab stride
-    const float* xsp = xsum + wg * 4u + t;  // chunk (ks*16 + i4*4 + wg)*4 + t of row 0
+    const uint32_t xs_adv = 256u * kpar;                            // chunk sums per k-slab stride (bytes)
+    uint32_t xsp = smem_addr(xsum) + lc0 * 4u;                      // chunk (ks*16 + i4*4 + wg)*4 + t of row 0
+    const uint32_t xs_row = cpr * 4u;
     float* gred = red + (size_t)grp * Red<MP>::GROUP_FLOATS;
 
     float acc[NT][4];
@@ -281,7 +304,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (kpar > 1u) {
 #pragma unroll
             for (int j = 0; j < NT; ++j) xb[j] += kp * (xadv[j] / kpar);
-            xsp += kp * 64u;
+            xsp += kp * 256u;
         }
         for (uint32_t ks = 0; ks < kslabs_v; ++ks) {
             const uint32_t stage = grp * nsg + c_kmod, parity = c_par;
@@ -290,27 +313,22 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 ok = mbar_wait(smem_addr(&full_bars[stage]), parity, &abort_flag, 0x10);
                 ok = __all_sync(0xFFFFFFFFu, ok);
             }
-            if (ok && !dbg_skip) {
-                const uint8_t* st = ring + (size_t)stage * STAGE_BYTES;
-                const uint16_t* sp = reinterpret_cast<const uint16_t*>(st + Q_BYTES);
-                const uint16_t* bp = reinterpret_cast<const uint16_t*>(st + Q_BYTES + SB_BYTES);
+            if (ok) {
+                const uint32_t st = ring_a + stage * (uint32_t)STAGE_BYTES;
+                uint32_t qa = st + q_lane, sa = st + sb_lane, lc = lc0;
+                uint32_t xa[NT];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) xa[j] = xb[j];
+                uint32_t xsa = xsp;
 #pragma unroll 1
                 for (uint32_t i4 = 0; i4 < 4u; ++i4) {
-                    const uint32_t lc = (i4 * 4u + wg) * 4u + t;  // chunk inside the slab row
-                    // past the end of K (linear mode only; tiled TMA zero-fills): a zero scale
-                    // and bias against zero-staged x contribute exactly 0
-                    uint32_t lcc = lc;
-                    bool valid = true;
-                    if (ktail) {  // CTA-uniform: only when K is shorter than one slab
-                        valid = lc < chunks;
-                        lcc = valid ? lc : 0u;
-                    }
-                    const uint4 q0 = *reinterpret_cast<const uint4*>(st + g * qpitch + lcc * 16u);
-                    const uint4 q1 = *reinterpret_cast<const uint4*>(st + (g + 8u) * qpitch + lcc * 16u);
-                    const uint32_t sbi = sbrow + ((lcc * CW) >> gshift);
-                    uint32_t s0 = sp[sbi], b0 = bp[sbi];
-                    uint32_t s1 = sp[sbi + 8u * spitch], b1 = bp[sbi + 8u * spitch];
-                    if (ktail && !valid) s0 = b0 = s1 = b1 = 0u;
+                    const uint4 q0 = lds128(qa);
+                    const uint4 q1 = lds128(qa + 8u * qpitch);
+                    uint32_t s0 = lds16(sa), b0 = lds16(sa + SB_BYTES);
+                    uint32_t s1 = lds16(sa + sb_row8), b1 = lds16(sa + sb_row8 + SB_BYTES);
+                    // past the end of K (linear mode with a short K only; tiled TMA zero-fills):
+                    // a zero scale and bias against zero-staged x contribute exactly 0
+                    if (ktail && lc >= chunks) s0 = b0 = s1 = b1 = 0u;
                     const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
                     const uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
                     // two independent accumulation chains (even / odd words), each started by
@@ -335,8 +353,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         }
 #pragma unroll
                         for (int j = 0; j < NT; ++j) {
-                            const uint4 xu = *reinterpret_cast<const uint4*>(
-                                xb[j] + i4 * (4u * STEP_UNITS * 16u) + wd * 16);
+                            const uint4 xu = lds128(xa[j] + wd * 16);
                             if (wd == 0) mma_bf16_z(d0[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
                             else if (wd == 1) mma_bf16_z(d1[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
                             else if (wd & 1) mma_bf16(d1[j], a[0], c[0], a[1], c[1], xu.x, xu.y);
@@ -352,11 +369,11 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         const float bt1 = __fmaf_rn(-OFF, sc1, __uint_as_float(b1 << 16));
 #pragma unroll
                         for (int j = 0; j < NT; ++j) {
-                            const float xs0 = xsp[(size_t)(2 * j) * cpr + i4 * 16u];
+                            const float xs0 = ldsf32(xsa + (2 * j) * xs_row);
                             acc[j][0] = __fmaf_rn(sc0, d0[j][0] + d1[j][0], __fmaf_rn(bt0, xs0, acc[j][0]));
                             acc[j][2] = __fmaf_rn(sc1, d0[j][2] + d1[j][2], __fmaf_rn(bt1, xs0, acc[j][2]));
                             if (2u * j + 1u < M) {  // CTA-uniform: the odd activation row exists
-                                const float xs1 = xsp[(size_t)(2 * j + 1) * cpr + i4 * 16u];
+                                const float xs1 = ldsf32(xsa + (2 * j + 1) * xs_row);
                                 acc[j][1] = __fmaf_rn(sc0, d0[j][1] + d1[j][1], __fmaf_rn(bt0, xs1, acc[j][1]));
                                 acc[j][3] = __fmaf_rn(sc1, d0[j][3] + d1[j][3], __fmaf_rn(bt1, xs1, acc[j][3]));
                             }
@@ -367,6 +384,13 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                             for (int e = 0; e < 4; ++e) acc[j][e] += d0[j][e] + d1[j][e];
                     }
+                    // next step of this warp: 4 steps (16 chunks) further along the row
+                    qa += 256u;
+                    sa += sb_step;
+                    lc += 16u;
+                    xsa += 64u;
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) xa[j] += 4u * STEP_UNITS * 16u;
                 }
             }
             if (ok) {
@@ -380,7 +404,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // back to k-slab 0 of the row
 #pragma unroll
         for (int j = 0; j < NT; ++j) xb[j] -= kslabs_v * xadv[j] + (kpar > 1u ? kp * (xadv[j] / kpar) : 0u);
-        xsp -= kslabs_v * xs_adv + (kpar > 1u ? kp * 64u : 0u);
+        xsp -= kslabs_v * xs_adv + (kpar > 1u ? kp * 256u : 0u);
 
         // ---- tile complete: quad sum (EXACT), then 4 partials per output through shared memory
         constexpr int WS = Red<MP>::WS;
@@ -522,7 +546,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
     const uint32_t gshift = group == 32 ? 5u : 6u;
     // K within one slab: plain bulk copies (rows of a tile are contiguous); else tiled TMA
-    const bool linear = K <= (uint32_t)KC && !(flags & 0x2000u);
+    const bool linear = K <= (uint32_t)KC && !(flags & MIORI_TUNE_GEMV_TILED);
     CUtensorMap tq, ts, tb;
     int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)K * BITS / 32, N,
                           ROW_BYTES / 4, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -544,8 +568,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
         if (e == cudaSuccess)                                                                    \
             e = launch(kern, dim3(grid), dim3(THREADS), smem, stream, pdl, tq, ts, tb, ql,       \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
-                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
-                       (flags & 0x1000u) ? 1u : 0u);        \
+                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar);        \
     } while (0)
     if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true); else MIORI_TMA_LAUNCH(false);
 #undef MIORI_TMA_LAUNCH

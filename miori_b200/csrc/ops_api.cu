@@ -31,8 +31,8 @@ int gemv_entry(const char* op, const void* q, const void* s, const void* b, cons
     if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
     if (!aligned16(x)) return fail(MIORI_E_INVALID, "%s: x must be 16-byte aligned", op);
     const bool force_exact = (flags & MIORI_GEMV_EXACT) != 0;
-    const bool force_simt = (flags & 0x400u) != 0;  // tuning override: shape-agnostic SIMT path
-    const bool no_bulk = (flags & 0x800u) != 0;     // tuning override: register-streaming kernel
+    const bool force_simt = (flags & MIORI_TUNE_GEMV_SIMT) != 0;  // tuning override: shape-agnostic SIMT path
+    const bool no_bulk = (flags & MIORI_TUNE_GEMV_LDG) != 0;     // tuning override: register-streaming kernel
     if (!force_simt && !(force_exact && M > 4)) {
         if (!no_bulk) {
             rc = gemvtma::try_launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
