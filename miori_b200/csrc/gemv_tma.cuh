@@ -47,13 +47,6 @@ struct Red {
     static constexpr int GROUP_FLOATS = 2 * 4 * WS;  // double-buffered, 4 warps
 };
 
-__device__ __forceinline__ uint32_t shr_mulhi(uint32_t w, int k) {
-    // w >> k on the integer-multiply pipe, leaving the ALU pipe to the LOP3s
-    uint32_t r;
-    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(1u << (32 - k)));
-    return r;
-}
-
 // Shared-memory loads by 32-bit shared address (one instruction each, no generic addressing).
 // volatile: the data arrives through TMA, so the loads must stay behind the mbarrier wait.
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
@@ -298,8 +291,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (uint32_t set0 = 0; warp < WARPS && set0 < ntiles; set0 += ngrp) {
         const uint32_t nt = min(ngrp, ntiles - set0);
         if (grp >= nt) break;
-        const uint32_t vt = set0 + grp, kp = vt % kpar;
-        const uint32_t tile = blockIdx.x + (vt / kpar) * gridDim.x;
+        const uint32_t vt = set0 + grp;
+        const uint32_t kp = kpar > 1u ? vt % kpar : 0u;
+        const uint32_t tile = blockIdx.x + (kpar > 1u ? vt / kpar : vt) * gridDim.x;
         // start at this group's first k-slab of the row
         if (kpar > 1u) {
 #pragma unroll
@@ -344,8 +338,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         uint32_t a[4], c[4];  // pairs (n0,n4),(n1,n5),(n2,n6),(n3,n7), rows g, g+8
 #pragma unroll
                         for (int p = 0; p < 4; ++p) {
-                            a[p] = lop3_and_or(p ? shr_mulhi(w0[wd], 4 * p) : w0[wd], MASK, MAGIC);
-                            c[p] = lop3_and_or(p ? shr_mulhi(w1[wd], 4 * p) : w1[wd], MASK, MAGIC);
+                            a[p] = lop3_and_or(w0[wd] >> (4 * p), MASK, MAGIC);
+                            c[p] = lop3_and_or(w1[wd] >> (4 * p), MASK, MAGIC);
                             if (!EXACT) {
                                 a[p] = bf16x2_fma(bf16x2_sub(a[p], MAGIC), s2a, b2a);
                                 c[p] = bf16x2_fma(bf16x2_sub(c[p], MAGIC), s2b, b2b);
