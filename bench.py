@@ -323,7 +323,9 @@ def main():
         ms = timed(graphs[M].replay, max(3, args.steps // 2)) / max(3, args.steps // 2)
         per_m[str(M)] = {"ms_per_pass": ms, "gbs": bytes_pass / (ms * 1e-3) / 1e9,
                          "us_per_launch": 1e3 * ms / launches_pass,
-                         "path": "gemv4 on packed int4" if M <= 8 else "tcgen05 GEMM on the bf16 cache"}
+                         "path": "gemv4 on packed int4" if M <= 8 else
+                         ("gemv4 on packed int4 (K<=2048), tcgen05 GEMM on the bf16 cache (K=8192)"
+                          if M <= 16 else "tcgen05 GEMM on the bf16 cache")}
 
     # ---- the same M=1 pass with the four projections of a layer on four concurrent streams
     # (no dependency between them): separates kernel throughput from launch-chain latency

@@ -179,10 +179,10 @@ int miori_gemm_bf16_cache_static(const void* A, const void* cache, void* C, uint
  *      projection to gemv4_b for narrow batches and to the bf16-cache GEMM otherwise. ------ */
 
 /* y[M][N] (fp32) = x[M][K] (bf16) x W^T.  M <= 8 streams the packed 4-bit weights
- * (miori_gemv4); wider M multiplies the bf16 cache on the tensor cores
- * (miori_gemm_bf16_cache_ws) when `cache` is given, else stays on the packed weights
- * (M <= 32).  The reference's cut-over is 4 rows; eight keep fp32-scale or bf16-weight GEMV
- * bandwidth-bound on this part. */
+ * (miori_gemv4), and so do 9..16 rows when K <= 2048; wider M multiplies the bf16 cache on the
+ * tensor cores (miori_gemm_bf16_cache_ws) when `cache` is given, else stays on the packed
+ * weights (M <= 32).  The reference's cut-over is 4 rows; here the packed path stays ahead
+ * further because it moves a quarter of the bytes. */
 int miori_linear4(const void* q, const void* s, const void* b, const void* cache, const void* x,
                   void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
                   void* workspace, size_t workspace_bytes, void* stream);

@@ -29,6 +29,9 @@ constexpr int BK = 64;        // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int GROUP_M = 16;   // row blocks per L2 group
 constexpr int THREADS = 192;
+// epilogue staging: each of the four epilogue warps owns two 32-row x 128-byte buffers
+constexpr int OUT_BUF_BYTES = 32 * 128;
+constexpr int OUT_STAGE_BYTES = 4 * 2 * OUT_BUF_BYTES;
 
 template <int BN>
 struct Cfg {
@@ -37,7 +40,7 @@ struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulators (256 or 512: powers of two)
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 /*alignment slack*/ + 256;
 };
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, 8-row
@@ -102,47 +105,75 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t m_blocks, u
     return c;
 }
 
-// Store 32 consecutive accumulator columns of one row: fp32 to C (or to the split-K partial
-// slice), or bf16 to C; columns at or past N are masked in groups of 4 / 8 (N % 8 == 0).
-template <bool OUT_BF16>
-__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], uint32_t row, uint32_t M,
-                                            uint32_t N, uint32_t col, void* Cout, float* part,
-                                            uint32_t splits) {
-    if (row >= M) return;
-    if (OUT_BF16 && splits == 1u) {
-        uint16_t* dst = reinterpret_cast<uint16_t*>(Cout) + (size_t)row * N + col;
+// Epilogue of one warp for one tile: its 32 accumulator rows (TMEM lanes) x BN columns go to
+// global memory through shared memory and TMA stores, 128 bytes of a row at a time (32 fp32 or
+// 64 bf16 columns).  Each lane writes its row's 128 bytes into a 32 x 128-byte buffer with the
+// 128-byte swizzle (conflict-free), lane 0 hands the buffer to the TMA engine, and the warp
+// moves on to its other buffer; the store clips rows >= M and columns >= N.  `fill` counts the
+// buffers this warp has handed over so far (selects the buffer and throttles reuse).
+template <bool OUT_BF16, int BN>
+__device__ __forceinline__ void epilogue_rows(uint32_t taddr, uint32_t row0, uint32_t col0,
+                                              uint32_t M, uint32_t N, bool bf16_out, uint32_t slice,
+                                              const CUtensorMap* tmap_c, uint32_t bufs,
+                                              uint32_t& fill, uint32_t lane) {
+    if (row0 >= M) return;
+    const uint32_t sw = lane & 7u;  // swizzle: 16-byte unit u of row r sits at unit u ^ (r & 7)
+    const uint32_t cols_per_fill = (OUT_BF16 && bf16_out) ? 64u : 32u;
+#pragma unroll 1
+    for (uint32_t c = 0; c < (uint32_t)BN && col0 + c < N; c += cols_per_fill) {
+        const uint32_t buf = bufs + (fill & 1u) * OUT_BUF_BYTES;
+        if (fill >= 2u) {  // the store issued two fills ago must have finished reading this buffer
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+        }
+        const uint32_t rowp = buf + lane * 128u;
+        uint32_t r[32];
+        tmem_ld32(taddr + c, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (OUT_BF16 && bf16_out) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (col + 8u * j < N) {
-                uint4 v;
-                v.x = float_to_bf16_bits(__uint_as_float(r[8 * j + 0])) |
-                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 1])) << 16);
-                v.y = float_to_bf16_bits(__uint_as_float(r[8 * j + 2])) |
-                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 3])) << 16);
-                v.z = float_to_bf16_bits(__uint_as_float(r[8 * j + 4])) |
-                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 5])) << 16);
-                v.w = float_to_bf16_bits(__uint_as_float(r[8 * j + 6])) |
-                      (float_to_bf16_bits(__uint_as_float(r[8 * j + 7])) << 16);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+            for (int h = 0; h < 2; ++h) {
+                if (h == 1) {
+                    tmem_ld32(taddr + c + 32u, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        v[e] = float_to_bf16_bits(__uint_as_float(r[8 * j + 2 * e])) |
+                               (float_to_bf16_bits(__uint_as_float(r[8 * j + 2 * e + 1])) << 16);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(rowp + ((((uint32_t)(4 * h + j)) ^ sw) << 4)), "r"(v[0]),
+                                   "r"(v[1]), "r"(v[2]), "r"(v[3])
+                                 : "memory");
+                }
             }
-        }
-    } else {
-        float* dst = (splits == 1u ? reinterpret_cast<float*>(Cout) : part) + (size_t)row * N + col;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (col + 4u * j < N)
-                *reinterpret_cast<uint4*>(dst + 4 * j) =
-                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            for (int j = 0; j < 8; ++j)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(rowp + ((((uint32_t)j) ^ sw) << 4)), "r"(r[4 * j]),
+                               "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                             : "memory");
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_3d(tmap_c, (int)(col0 + c), (int)row0, (int)slice, buf);
+            tma_store_commit();
+        }
+        ++fill;
     }
 }
 
 template <int BN, bool OUT_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cout,
-                         float* __restrict__ ws, uint32_t splits, uint32_t M, uint32_t N,
-                         uint32_t K) {
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_c, uint32_t splits, uint32_t M,
+                         uint32_t N, uint32_t K) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
@@ -150,7 +181,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     const uint32_t raw = smem_addr(smem_raw);
     const uint32_t tiles_base = (raw + 1023u) & ~1023u;            // 1024-byte aligned ring
-    const uint32_t bars = tiles_base + C::STAGES * C::STAGE_BYTES;  // barriers after the ring
+    const uint32_t out_stage = tiles_base + C::STAGES * C::STAGE_BYTES;  // epilogue staging
+    const uint32_t bars = out_stage + OUT_STAGE_BYTES;                    // barriers after it
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
@@ -178,6 +210,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -242,29 +275,25 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
     } else {
         const uint32_t quad = warp & 3u;  // TMEM lane quadrant this warp may read
-        uint32_t tile_it = 0;
+        const uint32_t bufs = out_stage + quad * 2u * OUT_BUF_BYTES;
+        uint32_t tile_it = 0, fill = 0;
         bool ok = true;
         for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
             const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
-            float* part = ws + (size_t)(t % splits) * M * N;  // used when splits > 1
             const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
             ok = mbar_wait(tfull_bar(acc), aph, &abort_flag, 4);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t row = tc.m_blk * BM + quad * 32u + lane;
-            const uint32_t col0 = tc.n_blk * BN;
-#pragma unroll 1
-            for (uint32_t c = 0; c < (uint32_t)BN; c += 32u) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                store_chunk<OUT_BF16>(r, row, M, N, col0 + c, Cout, part, splits);
-            }
+            // split-K partials are fp32 slices of the workspace; the last argument picks the slice
+            epilogue_rows<OUT_BF16, BN>(tmem_base + ((quad * 32u) << 16) + acc * BN,
+                                        tc.m_blk * BM + quad * 32u, tc.n_blk * BN, M, N,
+                                        splits == 1u, t % splits, &tmap_c, bufs, fill, lane);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
+        if (lane == 0) tma_store_wait_all();  // stores complete before shared memory goes away
     }
 
     // teardown: on abort give in-flight copies and MMAs time to land before freeing TMEM
@@ -300,7 +329,7 @@ constexpr int A_BYTES = BM * BK * 2;         // 16 KB: this CTA's 128 rows of A
 constexpr int B_BYTES = (BN / 2) * BK * 2;   // 16 KB: this CTA's 128 rows of B
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 2 * BN;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 + 256;
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -351,16 +380,17 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar_local) {
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                              const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cout,
-                              float* __restrict__ ws, uint32_t splits, uint32_t M, uint32_t N,
-                              uint32_t K) {
+                              const __grid_constant__ CUtensorMap tmap_b,
+                              const __grid_constant__ CUtensorMap tmap_c, uint32_t splits,
+                              uint32_t M, uint32_t N, uint32_t K) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
 
     const uint32_t raw = smem_addr(smem_raw);
     const uint32_t tiles_base = (raw + 1023u) & ~1023u;
-    const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
+    const uint32_t out_stage = tiles_base + STAGES * STAGE_BYTES;
+    const uint32_t bars = out_stage + OUT_STAGE_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
@@ -388,6 +418,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -458,29 +489,24 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
     } else {
         const uint32_t quad = warp & 3u;
-        uint32_t tile_it = 0;
+        const uint32_t bufs = out_stage + quad * 2u * OUT_BUF_BYTES;
+        uint32_t tile_it = 0, fill = 0;
         bool ok = true;
         for (uint32_t t = pair_id; t < tiles && ok; t += pairs, ++tile_it) {
             const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
-            float* part = ws + (size_t)(t % splits) * M * N;
             const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
             ok = mbar_wait(tfull_bar(acc), aph, &abort_flag, 0x24);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t row = tc.m_blk * 2 * BM + rank * BM + quad * 32u + lane;
-            const uint32_t col0 = tc.n_blk * BN;
-#pragma unroll 1
-            for (uint32_t c = 0; c < (uint32_t)BN; c += 32u) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((quad * 32u) << 16) + acc * BN + c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                store_chunk<OUT_BF16>(r, row, M, N, col0 + c, Cout, part, splits);
-            }
+            epilogue_rows<OUT_BF16, BN>(tmem_base + ((quad * 32u) << 16) + acc * BN,
+                                        tc.m_blk * 2 * BM + rank * BM + quad * 32u, tc.n_blk * BN,
+                                        M, N, splits == 1u, t % splits, &tmap_c, bufs, fill, lane);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(tempty_bar(acc));
         }
+        if (lane == 0) tma_store_wait_all();
     }
 
     __syncwarp();
@@ -546,14 +572,30 @@ static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
                         CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// Tensor map the epilogue stores through: C itself ([1][M][N], fp32 or bf16), or the split-K
+// workspace ([splits][M][N] fp32).  Boxes are 32 rows x 128 bytes with the 128-byte swizzle.
+static int make_tmap_out(CUtensorMap* map, void* Cm, float* ws, uint32_t M, uint32_t N,
+                         uint32_t splits, bool bf16) {
+    if (splits > 1)
+        return make_tmap_3d(map, ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, N, M, splits, 32, 32,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+    if (bf16)
+        return make_tmap_3d(map, Cm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, 1, 64, 32,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+    return make_tmap_3d(map, Cm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, N, M, 1, 32, 32,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 // Launch the two-CTA kernel: clusters of 2, one pair per SM pair.
 static int launch_gemm_pair(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N,
                             uint32_t K, uint32_t flags, float* ws, uint32_t splits,
                             cudaStream_t stream) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     int rc = make_tmap(&ta, A, M, K, BM);
     if (rc) return rc;
     rc = make_tmap(&tb, Bc, N, K, pair::BN / 2);
+    if (rc) return rc;
+    rc = make_tmap_out(&tc, Cm, ws, M, N, splits, (flags & MIORI_OUT_BF16) != 0);
     if (rc) return rc;
     const uint32_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + pair::BN - 1) / pair::BN) * splits;
     uint32_t pairs = (uint32_t)sm_count() / 2;
@@ -577,11 +619,11 @@ static int launch_gemm_pair(const void* A, const void* Bc, void* Cm, uint32_t M,
     if (bf16) {
         auto kern = pair::gemm_bf16_tcgen05_pair_kernel<true>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cm, ws, splits, M, N, K);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, splits, M, N, K);
     } else {
         auto kern = pair::gemm_bf16_tcgen05_pair_kernel<false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, ta, tb, Cm, ws, splits, M, N, K);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, splits, M, N, K);
     }
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05_pair launch");
     return MIORI_OK;
@@ -608,10 +650,12 @@ template <int BN>
 static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N, uint32_t K,
                        uint32_t flags, float* ws, uint32_t splits, cudaStream_t stream) {
     using C = Cfg<BN>;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     int rc = make_tmap(&ta, A, M, K, BM);
     if (rc) return rc;
     rc = make_tmap(&tb, Bc, N, K, BN);
+    if (rc) return rc;
+    rc = make_tmap_out(&tc, Cm, ws, M, N, splits, (flags & MIORI_OUT_BF16) != 0);
     if (rc) return rc;
     const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     uint32_t grid = (uint32_t)sm_count();
@@ -623,13 +667,13 @@ static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e == cudaSuccess)
             e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
-                       Cm, ws, splits, M, N, K);
+                       tc, splits, M, N, K);
     } else {
         auto kern = gemm_bf16_tcgen05_kernel<BN, false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e == cudaSuccess)
             e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
-                       Cm, ws, splits, M, N, K);
+                       tc, splits, M, N, K);
     }
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05 launch");
     if (splits > 1) return launch_reduce(Cm, M, N, flags, ws, splits, stream);

@@ -43,6 +43,25 @@ inline int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType 
     return MIORI_OK;
 }
 
+// Row-major 3-D tensor [d2][d1][d0] (d0 innermost), box [1][box1][box0], no fill (used for
+// stores, which clip at the tensor's edges).  d0*esize and d1*d0*esize must be multiples of 16
+// bytes and the base 16-byte aligned.
+inline int make_tmap_3d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
+                        uint32_t esize, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box0,
+                        uint32_t box1, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {d0 * esize, d0 * d1 * esize};
+    const cuuint32_t box[3] = {box0, box1, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled (3-D) failed (%d)", (int)r);
+    return MIORI_OK;
+}
+
 #ifdef __CUDACC__
 // 2-D tiled TMA load into shared memory; c0 is the innermost (element) coordinate, whose
 // byte offset must be a multiple of 16.  Completion is counted in bytes on `bar`.
@@ -53,6 +72,29 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         " [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
+}
+
+// 3-D tiled TMA store from shared memory (bulk-group completion).  c0 is the innermost
+// coordinate (byte offset a multiple of 16, never negative); elements outside the tensor are
+// not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2,
+                                             uint32_t src) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+        ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(src)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// wait until at most N of this thread's bulk groups still read their shared-memory source
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// wait until every bulk group of this thread has completed (its writes are performed)
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 #endif
 

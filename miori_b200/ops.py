@@ -99,7 +99,8 @@ def gemm_bf16_cache(A, cache, N, flags=0, out=None, workspace=None):
 
 
 def linear4(q, s, b, cache, x, group=32, flags=0, out=None, workspace=None):
-    """Projection dispatch (packed-weight GEMV for M <= 8, bf16-cache GEMM above)."""
+    """Projection dispatch (packed-weight GEMV for M <= 8, and M <= 16 while K <= 2048; bf16-cache
+    GEMM above)."""
     _need_cuda(q, s, b, x)
     M, K = x.shape
     N = q.shape[0]

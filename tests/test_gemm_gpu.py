@@ -127,10 +127,11 @@ def test_split_k_with_workspace_matches_oracle(port, M, N, K):
     assert miori_b200.lib.miori_device_error_poll() == 0
 
 
-@pytest.mark.parametrize("M", [1, 4, 8, 9, 32])
+@pytest.mark.parametrize("M", [1, 4, 8, 9, 16, 17, 32])
 def test_linear_dispatch(port, M):
-    """miori_linear4 routes M <= 8 to the packed-weight GEMV and wider M to the cache GEMM
-    (the reference's BatchEngine::linear policy, src/batch.cpp:223-230)."""
+    """miori_linear4 routes narrow batches (M <= 8, and M <= 16 while K <= 2048) to the
+    packed-weight GEMV and wider M to the cache GEMM (the reference's BatchEngine::linear
+    policy, src/batch.cpp:223-230, with a later cut-over)."""
     N, K = 3072, 2048
     q, s, b, cache = _weights(N, K, 64, seed=31)
     x = synth.make_activation(M, K, seed=32, device=DEV)
@@ -141,5 +142,5 @@ def test_linear_dispatch(port, M):
     want = port.gemv(4, u32(q), u16(s), u16(b), u16(x), 64)
     assert_close(y.cpu().numpy(), want, what=f"linear4 M={M}")
     assert_close(y_nocache.cpu().numpy(), want, what=f"linear4 (no cache) M={M}")
-    if M <= 8:
+    if M <= 16:
         assert torch.equal(y, miori_b200.gemv4(q, s, b, x, group=64))
