@@ -223,24 +223,42 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
 
-    pdl_wait_prior();  // A may be produced, and C read, by the preceding kernel
+    // A may be produced, and C read, by the preceding kernel.  The cache is immutable, so the
+    // producer first issues the B tiles of its first k-blocks (the ring is empty: no waits) and
+    // only then joins the wait; under programmatic dependent launch that fetch overlaps the
+    // predecessor's tail.
+    if (threadIdx.x != 0) pdl_wait_prior();
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, pre = 0;
             bool ok = true;
+            if (blockIdx.x < tiles) {
+                const TileCoord tc = tile_coord(blockIdx.x / splits, m_blocks, n_blocks);
+                const uint32_t sp = blockIdx.x % splits;
+                const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
+                pre = min((uint32_t)C::STAGES, kb1 - kb0);
+                for (uint32_t i = 0; i < pre; ++i) {
+                    mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+                    tma_load_2d(tiles_base + i * C::STAGE_BYTES + C::A_BYTES, &tmap_b,
+                                (int)((kb0 + i) * BK), (int)(tc.n_blk * BN), full_bar(i));
+                }
+            }
+            pdl_wait_prior();
             for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
                 const uint32_t sp = t % splits;
                 const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
                 for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 1))) break;
-                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
                     const uint32_t sa = tiles_base + s * C::STAGE_BYTES;
+                    if (it >= pre) {
+                        if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 1))) break;
+                        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                        tma_load_2d(sa + C::A_BYTES, &tmap_b, (int)(kb * BK), (int)(tc.n_blk * BN),
+                                    full_bar(s));
+                    }
                     tma_load_2d(sa, &tmap_a, (int)(kb * BK), (int)(tc.m_blk * BM), full_bar(s));
-                    tma_load_2d(sa + C::A_BYTES, &tmap_b, (int)(kb * BK), (int)(tc.n_blk * BN),
-                                full_bar(s));
                 }
             }
         }
@@ -432,28 +450,44 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
 
-    pdl_wait_prior();
+    if (threadIdx.x != 0) pdl_wait_prior();
 
     if (warp == 0) {
         if (lane == 0) {
             // producer of this CTA: its A rows and its half of the B rows, both completing on
-            // the leader's full barrier
-            uint32_t it = 0;
+            // the leader's full barrier.  As in the single-CTA kernel the B tiles of the first
+            // k-blocks are issued before the dependency wait.
+            uint32_t it = 0, pre = 0;
             bool ok = true;
+            if (pair_id < tiles) {
+                const TileCoord tc = tile_coord(pair_id / splits, m_blocks, n_blocks);
+                const uint32_t sp = pair_id % splits;
+                const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
+                pre = min((uint32_t)STAGES, kb1 - kb0);
+                for (uint32_t i = 0; i < pre; ++i) {
+                    if (rank == 0) mbar_expect_tx(full_bar(i), 2u * STAGE_BYTES);
+                    tma_load_2d_pair(tiles_base + i * STAGE_BYTES + A_BYTES, &tmap_b,
+                                     (int)((kb0 + i) * BK), (int)(tc.n_blk * BN + rank * (BN / 2)),
+                                     full_bar(i) & PEER_MASK);
+                }
+            }
+            pdl_wait_prior();
             for (uint32_t t = pair_id; t < tiles && ok; t += pairs) {
                 const TileCoord tc = tile_coord(t / splits, m_blocks, n_blocks);
                 const uint32_t sp = t % splits;
                 const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
                 for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 0x21))) break;
-                    if (rank == 0) mbar_expect_tx(full_bar(s), 2u * STAGE_BYTES);
                     const uint32_t sa = tiles_base + s * STAGE_BYTES;
                     const uint32_t fb = full_bar(s) & PEER_MASK;
+                    if (it >= pre) {
+                        if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 0x21))) break;
+                        if (rank == 0) mbar_expect_tx(full_bar(s), 2u * STAGE_BYTES);
+                        tma_load_2d_pair(sa + A_BYTES, &tmap_b, (int)(kb * BK),
+                                         (int)(tc.n_blk * BN + rank * (BN / 2)), fb);
+                    }
                     tma_load_2d_pair(sa, &tmap_a, (int)(kb * BK),
                                      (int)(tc.m_blk * 2 * BM + rank * BM), fb);
-                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, (int)(kb * BK),
-                                     (int)(tc.n_blk * BN + rank * (BN / 2)), fb);
                 }
             }
         }
@@ -550,19 +584,6 @@ splitk_reduce_kernel(const float4* __restrict__ ws, void* __restrict__ Cout, siz
             reinterpret_cast<float4*>(Cout)[i] = a;
         }
     }
-}
-
-// Number of K splits worth using: only when the output tiles alone would leave most SMs idle
-// (the partials cost a second kernel and 8 bytes of traffic per output element per split),
-// never fewer than 4 k-blocks per split, at most 16.
-static uint32_t choose_splits(uint32_t tiles, uint32_t k_blocks, size_t ws_bytes, size_t mn) {
-    const uint32_t sms = (uint32_t)sm_count();
-    if (tiles * 3 > sms || k_blocks < 8) return 1;  // only when under a third of the SMs have a tile
-    uint32_t s = (sms + tiles - 1) / tiles;
-    s = std::min<uint32_t>(s, k_blocks / 4);
-    s = std::min<uint32_t>(s, 16);
-    if (mn) s = (uint32_t)std::min<size_t>(s, ws_bytes / (mn * 4));
-    return s < 2 ? 1 : s;
 }
 
 // [rows][K] bf16 row-major, box = [box_rows][64], 128-byte swizzle, zero fill out of range.
@@ -699,20 +720,56 @@ struct GemmPlan {
     bool pair;   // 256 x 256 tiles on SM pairs (two-CTA kernel)
     uint32_t splits;
 };
+
+// The plan is the cheapest of {128x128, 128x256, 256x256-on-pairs} x {1..16 K-splits} under a
+// small cost model (microseconds):
+//   main loop  = waves x k-blocks per work item x time per k-block of that tile shape, where
+//                waves = ceil(work items / SMs or SM pairs) -- but never less than the time
+//                HBM needs to deliver the cache and A once;
+//   split cost = a second (reduction) kernel plus (splits + 1) passes over M x N fp32.
+// The per-k-block times are what the kernels sustain on a B200 when L2 feeds them (bigger tiles
+// need fewer bytes per flop): 0.31 us for 128x128, 0.375 us for 128x256, 0.315 us for a
+// 256x256 pair tile.  Splitting K therefore happens when the tiles alone would leave most SMs
+// idle and K is long enough to pay for the reduction, never below 4 k-blocks per split.
 static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, size_t ws_bytes) {
-    const uint32_t m_blocks = (M + BM - 1) / BM;
-    const uint32_t tiles256 = m_blocks * ((N + 255) / 256);
-    GemmPlan p;
-    // Wide tiles amortise B traffic; narrow ones fill the SMs when there are few tiles.
-    p.wide = (tiles256 >= (uint32_t)sm_count() && !(flags & MIORI_TUNE_GEMM_NARROW)) || (flags & MIORI_TUNE_GEMM_WIDE);
-    // SM pairs when there are enough 256 x 256 tiles to occupy them (tuning flags: 0x4000
-    // forces the pair kernel, 0x8000 forbids it)
-    const uint32_t tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
-    p.pair = ((tiles_pair * 2 >= (uint32_t)sm_count() / 2 && M > 128 && !(flags & 0x300u)) ||
-              (flags & MIORI_TUNE_GEMM_PAIR)) && !(flags & MIORI_TUNE_GEMM_NOPAIR);
-    const uint32_t tiles = p.pair ? 2 * tiles_pair : (p.wide ? tiles256 : m_blocks * ((N + 127) / 128));
-    p.splits = ws_bytes ? choose_splits(tiles, K / BK, ws_bytes, (size_t)M * N) : 1;
-    return p;
+    const uint32_t sms = (uint32_t)sm_count();
+    const uint32_t k_blocks = K / BK;
+    const size_t mn = (size_t)M * N;
+    struct Shape {
+        bool wide, pair, allowed;
+        uint32_t tiles, units;
+        double t_kb;
+    };
+    const uint32_t m128 = (M + 127) / 128, m256 = (M + 255) / 256;
+    const uint32_t n128 = (N + 127) / 128, n256 = (N + 255) / 256;
+    const bool force_narrow = flags & MIORI_TUNE_GEMM_NARROW, force_wide = flags & MIORI_TUNE_GEMM_WIDE;
+    const bool force_pair = flags & MIORI_TUNE_GEMM_PAIR, no_pair = flags & MIORI_TUNE_GEMM_NOPAIR;
+    const bool forced = force_narrow || force_wide || force_pair;
+    Shape shapes[3] = {
+        {false, false, !forced || force_narrow, m128 * n128, sms, 0.31},
+        {true, false, !forced || force_wide, m128 * n256, sms, 0.375},
+        {false, true, ((!forced && M > 128) || force_pair) && !no_pair, m256 * n256, sms / 2, 0.315},
+    };
+    const double t_hbm = ((double)N * K * 2 + (double)M * K * 2) / 6.5e6;  // us at 6.5 TB/s
+    uint32_t max_s = std::min<uint32_t>(16, std::max<uint32_t>(1, k_blocks / 4));
+    if (!ws_bytes) max_s = 1;
+    else if (mn) max_s = (uint32_t)std::min<size_t>(max_s, std::max<size_t>(1, ws_bytes / (mn * 4)));
+    GemmPlan best = {false, false, 1};
+    double best_t = 1e30;
+    for (const Shape& sh : shapes) {
+        if (!sh.allowed) continue;
+        for (uint32_t sp = 1; sp <= max_s; ++sp) {
+            const uint32_t waves = (sh.tiles * sp + sh.units - 1) / sh.units;
+            double t = (double)waves * ((k_blocks + sp - 1) / sp) * sh.t_kb;
+            if (t < t_hbm) t = t_hbm;
+            if (sp > 1) t += 2.0 + (double)(sp + 1) * mn * 4 / 5e6;
+            if (t < best_t * 0.97) {  // a later candidate must win by 3 %: prefers fewer splits
+                best_t = t;
+                best = {sh.wide, sh.pair, sp};
+            }
+        }
+    }
+    return best;
 }
 
 static int run_plan(const GemmPlan& p, const void* A, const void* cache, void* Cm, uint32_t M,

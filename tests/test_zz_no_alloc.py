@@ -57,10 +57,11 @@ def test_static_scratch_matches_workspace_entry_twice(M, N, K):
 def test_shape_without_split_runs_and_oversized_split_is_refused():
     A, cache = _problem(300, 256, 128, seed=9)  # too short a K to split: no scratch involved
     assert torch.equal(_static(A, cache, 256), miori_b200.gemm_bf16_cache(A, cache, 256))
-    # With the wide-tile tuning flag, 512 x 3072 splits K in four: 4 x 6 MiB of partials, more
-    # than the built-in 16 MiB.  The entry refuses before touching any pointer.
-    M, N, K, wide = 512, 3072, 2048, 0x200
-    rc = lib.miori_gemm_bf16_cache_static(0x1000, 0x1000, 0x1000, M, N, K, wide, None)
+    # 1024 x 2304 with a very long K has 36 pair tiles for 74 SM pairs, so it splits K in two:
+    # 2 x 9 MiB of partials, more than the built-in 16 MiB.  The entry refuses before touching
+    # any pointer.
+    M, N, K = 1024, 2304, 32768
+    rc = lib.miori_gemm_bf16_cache_static(0x1000, 0x1000, 0x1000, M, N, K, 0, None)
     assert rc == -1
     msg = lib.miori_last_error().decode()
     assert "scratch" in msg and "miori_gemm_bf16_cache_ws" in msg and str(16 << 20) in msg
