@@ -192,6 +192,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--allgather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: gather y by peer stores from the GEMV epilogue (default) or with "
+                         "ncclAllGather after each launch")
     ap.add_argument("--eager", action="store_true",
                     help="launch the passes directly instead of replaying CUDA graphs (for a "
                          "profiler's launch list; timings then include host launch overhead)")
@@ -243,7 +246,23 @@ def main():
     MMAX = max(M_SWEEP)
     x_dev = {M: [synth.make_activation(M, K, seed=50 + M, device=dev) for _, K in SHAPES] for M in M_SWEEP}
     y_loc = {M: [torch.empty((M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
-    y_all = {M: [torch.empty((world * M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
+    # N > 1: the gathered outputs.  "peer": y[M][N] at the same offset of every rank's arena,
+    # written by all ranks' GEMV epilogues over NVLink; "nccl": rank-major blocks from ncclAllGather
+    grp, y_off, gather = None, None, "none"
+    if world > 1 and args.allgather == "peer":
+        from miori_b200.peers import PeerGroup
+        try:
+            grp = PeerGroup(rank, world, 16 << 20, dev)
+            gather = "peer stores fused in the GEMV epilogue"
+        except RuntimeError as e:
+            say(f"peer mapping unavailable ({e}); using ncclAllGather")
+    if grp is not None:
+        y_off = {M: [grp.alloc(M * N * 4) for N, _ in SHAPES] for M in M_SWEEP}
+        y_all = {M: [grp.tensor(o, (M, N)) for o, (N, _) in zip(y_off[M], SHAPES)] for M in M_SWEEP}
+    else:
+        if world > 1:
+            gather = "ncclAllGather after each launch"
+        y_all = {M: [torch.empty((world * M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
 
     # bf16 caches for the wide-batch path (M > 8 goes through the cache GEMM, the reference's
     # own policy for wide batches) and one split-K workspace shared by the in-order launches
@@ -251,11 +270,21 @@ def main():
     ws_bytes = max(lib.miori_gemm_workspace_bytes(M, N // world, K) for M in M_SWEEP for N, K in SHAPES)
     ws = torch.empty(max(ws_bytes // 4, 4), dtype=torch.float32, device=dev)
 
+    def packed_path(M, K):  # miori_linear4's own rule
+        return M <= 8 or (M <= 16 and K <= 2048)
+
     def one_pass(M):
         for projs, cs in zip(stack, caches):
-            for (q, s, b), c, x, y, ya in zip(projs, cs, x_dev[M], y_loc[M], y_all[M]):
+            for i, ((q, s, b), c, x, y, ya) in enumerate(zip(projs, cs, x_dev[M], y_loc[M], y_all[M])):
+                N, K = SHAPES[i]
+                if grp is not None and packed_path(M, K):
+                    grp.gemv_allgather(4, q, s, b, x, y_off[M][i], rank * (N // world), N, group=G,
+                                       flags=pdl)
+                    continue
                 miori_b200.linear4(q, s, b, c, x, group=G, flags=pdl, out=y, workspace=ws)
-                if world > 1:
+                if grp is not None:
+                    grp.allgather(y, y_off[M][i], rank * (N // world), N, flags=pdl)
+                elif world > 1:
                     dist.all_gather_into_tensor(ya, y)
 
     # ---- capture one CUDA graph per M
@@ -280,6 +309,16 @@ def main():
             one_pass(M)
         graphs[M] = g
     launches_pass = layers * len(SHAPES)
+
+    def kernels_in_pass(M):  # this library's kernel launches in one pass at M rows, on one rank
+        n = 0
+        for N, K in SHAPES:
+            if packed_path(M, K):
+                n += 1
+                continue
+            n += 2 if lib.miori_gemm_workspace_bytes(M, N // world, K) else 1  # GEMM (+ K-split sum)
+            n += 1 if grp is not None else 0                                      # peer all-gather
+        return layers * n
     say("graphs captured")
 
     def step():
@@ -360,7 +399,7 @@ def main():
     host_x, host_y = {}, {}
     for M in M_SWEEP:
         host_x[M] = [x.cpu().pin_memory() for x in x_dev[M]]
-        host_y[M] = [torch.empty((world * M, N // world)).pin_memory() if world > 1
+        host_y[M] = [torch.empty((world * M, N // world)).pin_memory() if world > 1 and grp is None
                      else torch.empty((M, N)).pin_memory() for N, _ in SHAPES]
         h2d += sum(t.numel() * 2 for t in host_x[M])
         d2h += sum(t.numel() * 4 for t in host_y[M])
@@ -398,10 +437,10 @@ def main():
         "metric": "int4 GEMV effective HBM GB/s (M=1-32)", "value": value, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(args, world),
+        "data": "synthetic", "config": dict(workload_config(args, world), allgather=gather),
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
-        "gpu_launches": args.steps * len(M_SWEEP) * launches_pass,
+        "gpu_launches": args.steps * sum(kernels_in_pass(M) for M in M_SWEEP),
         "per_m": per_m, "roofline": roofline, "clocks": clocks,
     }
 
@@ -416,6 +455,11 @@ def main():
         # Captured graphs hold NCCL work and tearing the communicator down under them can block;
         # every rank has finished the same work here, so leave without the teardown.
         torch.cuda.synchronize()
+        if grp is not None:
+            try:
+                grp.status()
+            except Exception as e:
+                print(f"[bench rank {rank}] {e}", file=sys.stderr, flush=True)
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()

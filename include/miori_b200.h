@@ -187,6 +187,49 @@ int miori_linear4(const void* q, const void* s, const void* b, const void* cache
                   void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- multi-GPU: N-sharded GEMV with the all-gather of y fused into the kernel.  The reference
+ *      runs on one GPU and has no counterpart; the partition follows its operand layout (rows of
+ *      q, s, b are independent: shaders/ops.metal:6-42), so rank r multiplies rows
+ *      [row0, row0 + n_local) and every rank ends up with the whole y. --------------------------- */
+
+/* One per rank (one process per GPU).  Each rank allocates an arena of device memory that every
+ * other rank maps through CUDA IPC; outputs live at the same offset in every arena.  create
+ * allocates and zeroes the arena on the current device; handle exports the 64-byte token
+ * (miori_peers_handle_bytes) the host passes to the other ranks by any channel; connect takes the
+ * tokens of all ranks in rank order (`world` x 64 bytes, this rank's own entry ignored). */
+typedef struct miori_peers miori_peers;
+int miori_peers_create(int rank, int world, size_t arena_bytes, miori_peers** out);
+size_t miori_peers_handle_bytes(void);
+int miori_peers_handle(miori_peers* g, void* handle_out);
+int miori_peers_connect(miori_peers* g, const void* handles);
+void* miori_peers_arena(miori_peers* g);        /* local arena (device pointer), offset 0 */
+size_t miori_peers_arena_bytes(miori_peers* g);
+/* MIORI_E_DEVICE if a kernel on this rank gave up waiting for a peer (bounded waits, about a
+ * second); the group is unusable afterwards. */
+int miori_peers_status(miori_peers* g);
+/* Call only when no rank has kernels in flight that store into this rank's arena. */
+int miori_peers_destroy(miori_peers* g);
+
+/* miori_gemv4 / miori_gemv8 on this rank's n_local rows of an n_total-row weight matrix (q, s, b
+ * point at the shard), writing y[m][row0 + n] at y_offset of EVERY rank's arena with peer stores
+ * from the epilogue.  When the kernel completes on a rank, all ranks' rows have arrived there.
+ * Every rank must enqueue the same sequence of *_allgather / miori_allgather calls on its
+ * group; x may be any device pointer, also one inside the arena.  y is fp32 [M][n_total] (bf16
+ * with MIORI_OUT_BF16).  Requires (K / group) % 8 == 0; other shapes get MIORI_E_INVALID. */
+int miori_gemv4_allgather(miori_peers* g, const void* q, const void* s, const void* b, const void* x,
+                          size_t y_offset, uint32_t n_local, uint32_t row0, uint32_t n_total,
+                          uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream);
+int miori_gemv8_allgather(miori_peers* g, const void* q, const void* s, const void* b, const void* x,
+                          size_t y_offset, uint32_t n_local, uint32_t row0, uint32_t n_total,
+                          uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream);
+/* All-gather for outputs of other kernels (e.g. the cache GEMM on an N-sharded cache): copies this
+ * rank's block src[M][n_local] (contiguous rows, elements of elem_bytes = 2 or 4) into columns
+ * [row0, row0 + n_local) of y[M][n_total] at y_offset of every rank's arena, its own included.
+ * Same ordering guarantees as above. */
+int miori_allgather(miori_peers* g, const void* src, size_t y_offset, uint32_t M, uint32_t n_local,
+                    uint32_t row0, uint32_t n_total, uint32_t elem_bytes, uint32_t flags,
+                    void* stream);
+
 /* Non-zero if a kernel of this library recorded an internal error on the current
  * device since the last call (bounded wait expired); clears the record. */
 int miori_device_error_poll(void);

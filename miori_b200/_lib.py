@@ -51,6 +51,17 @@ _SIGS = {
     "miori_gemm_static_scratch_bytes": (_sz, []),
     "miori_gemm_bf16_cache_static": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
     "miori_linear4": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p, _sz, _p]),
+    "miori_peers_create": (_i, [_i, _i, _sz, C.POINTER(_p)]),
+    "miori_peers_handle_bytes": (_sz, []),
+    "miori_peers_handle": (_i, [_p, _p]),
+    "miori_peers_connect": (_i, [_p, _p]),
+    "miori_peers_arena": (_p, [_p]),
+    "miori_peers_arena_bytes": (_sz, [_p]),
+    "miori_peers_status": (_i, [_p]),
+    "miori_peers_destroy": (_i, [_p]),
+    "miori_gemv4_allgather": (_i, [_p, _p, _p, _p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_gemv8_allgather": (_i, [_p, _p, _p, _p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_allgather": (_i, [_p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_device_error_poll": (_i, []),
 }
 

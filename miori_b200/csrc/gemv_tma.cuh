@@ -19,6 +19,7 @@
 #pragma once
 #include "common.cuh"
 #include "gemv_mma.cuh"
+#include "peers.cuh"
 #include "tma_host.cuh"
 
 #include <algorithm>
@@ -124,14 +125,15 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
     }
 }
 
-template <int BITS, bool EXACT, int NT, bool OUT_BF16>
+template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED>
 __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_s,
                 const __grid_constant__ CUtensorMap tmap_b, const uint8_t* __restrict__ qlin,
                 const uint16_t* __restrict__ slin, const uint16_t* __restrict__ blin,
                 const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
-                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar) {
+                uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar,
+                const PeerArgs pa, uint32_t n_total, uint32_t row0, size_t y_off) {
     using namespace gemvmma;
     const uint32_t nstage = ngrp * nsg;  // every active group owns a private ring of nsg stages
     constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
@@ -240,6 +242,33 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
 
     pdl_wait_prior();  // x (and y) belong to the predecessor until here
+
+    // N-sharded launch (pa.world > 1): this rank's rows [row0, row0 + N) of an n_total-row output
+    // go to every rank's copy of y (at y_off in each arena); peers.cuh has the three-counter
+    // protocol.  Everything it needs is re-read from the kernel parameters and the control block
+    // at the point of use, so the single-GPU path carries no extra registers through the loop.
+    // a template parameter rather than a run-time test: the single-GPU instantiation then
+    // compiles exactly as if the peer path did not exist (a run-time branch cost 3-16 %)
+    const uint32_t world = SHARDED ? pa.world : 0u;
+    if (world > 1u && blockIdx.x == 0 && threadIdx.x == 0) peer_announce_ready(pa, peer_epoch(pa));
+    // one output element: y[m][row0 + row] here and, when sharded, on every peer; `first` is
+    // true for the calling thread's first tile (it then waits for the peers' go-ahead)
+    auto store_out = [&](uint32_t m, uint32_t row, float v, bool first) {
+        const size_t idx = (size_t)m * n_total + row0 + row;
+        if (world <= 1u) {
+            if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)float_to_bf16_bits(v);
+            else reinterpret_cast<float*>(y)[idx] = v;
+            return;
+        }
+        if constexpr (SHARDED) {
+            if (first) peer_wait_ready(pa, peer_epoch(pa));
+            for (uint32_t p = 0; p < world; ++p) {
+                uint8_t* yp = peer_arena(pa, p) + y_off;
+                if (OUT_BF16) reinterpret_cast<uint16_t*>(yp)[idx] = (uint16_t)float_to_bf16_bits(v);
+                else reinterpret_cast<float*>(yp)[idx] = v;
+            }
+        }
+    };
 
     stage_x_padded<BITS, EXACT, MP>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
@@ -446,10 +475,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (kpar > 1u) {
                 if (w == 0) kred[((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP) + o] = v;
             } else if (w == 0 && m < M && row < N && ok) {
-                if (OUT_BF16)
-                    reinterpret_cast<uint16_t*>(y)[(size_t)m * N + row] = (uint16_t)float_to_bf16_bits(v);
-                else
-                    reinterpret_cast<float*>(y)[(size_t)m * N + row] = v;
+                store_out(m, row, v, tile_it == 0u);
             }
         }
         if (kpar > 1u) {
@@ -461,12 +487,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     float v = kr[o];
                     for (uint32_t j = 1; j < kpar; ++j) v += kr[(size_t)j * (16 * MP) + o];
                     const uint32_t r = o & 15u, m = o >> 4, row = tile * 16u + r;
-                    if (m < M && row < N && ok) {
-                        if (OUT_BF16)
-                            reinterpret_cast<uint16_t*>(y)[(size_t)m * N + row] = (uint16_t)float_to_bf16_bits(v);
-                        else
-                            reinterpret_cast<float*>(y)[(size_t)m * N + row] = v;
-                    }
+                    if (m < M && row < N && ok) store_out(m, row, v, tile_it == 0u);
                 }
             }
         }
@@ -478,6 +499,10 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (abort_flag) {  // let copies still in flight land before the CTA's memory is released
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+    }
+    if (world > 1u) {  // every thread of the CTA gets here: no early exits above
+        __syncthreads();
+        if (threadIdx.x == 0) peer_finish(pa, peer_epoch(pa));
     }
 }
 
@@ -492,6 +517,14 @@ size_t fixed_smem(uint32_t K) {
     bytes += (size_t)2 * GROUPS * 16 * MP * 4;  // partial outputs of groups that share a tile
     return bytes;
 }
+
+// Placement of an N-sharded launch's output: peers (world <= 1: none, y is a plain pointer),
+// rows of the whole output, this rank's first row, and the offset of y inside every arena.
+struct Shard {
+    PeerArgs pa = {};
+    uint32_t n_total = 0, row0 = 0;
+    size_t y_off = 0;
+};
 
 // Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
 // take the problem.
@@ -533,7 +566,7 @@ Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
 template <int BITS, bool EXACT, int NT>
 int launch_one(Plan plan, const void* q, const void* s, const void* b, const void* x, void* y,
                uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
-               cudaStream_t stream) {
+               cudaStream_t stream, const Shard& sh) {
     constexpr int KC = 16 * 4 * (128 / BITS);
     const size_t smem = fixed_smem<BITS, EXACT, NT>(K) + (size_t)plan.ngrp * plan.nsg * STAGE_BYTES;
     const uint32_t grid = plan.grid;
@@ -553,18 +586,24 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     if (rc) return rc;
     const uint8_t* ql = linear ? reinterpret_cast<const uint8_t*>(q) : nullptr;
     cudaError_t e;
-#define MIORI_TMA_LAUNCH(OB)                                                                     \
+#define MIORI_TMA_LAUNCH(OB, SH)                                                                 \
     do {                                                                                         \
-        auto kern = gemv_tma_kernel<BITS, EXACT, NT, OB>;                                        \
+        auto kern = gemv_tma_kernel<BITS, EXACT, NT, OB, SH>;                                    \
         e = cudaSuccess;                                                                         \
         if (smem > 48 * 1024)                                                                    \
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e == cudaSuccess)                                                                    \
             e = launch(kern, dim3(grid), dim3(THREADS), smem, stream, pdl, tq, ts, tb, ql,       \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
-                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar);        \
+                       reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
+                       sh.pa, sh.pa.world > 1 ? sh.n_total : N, sh.pa.world > 1 ? sh.row0 : 0u, sh.y_off); \
     } while (0)
-    if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true); else MIORI_TMA_LAUNCH(false);
+    const bool sharded = sh.pa.world > 1;
+    if (flags & MIORI_OUT_BF16) {
+        if (sharded) MIORI_TMA_LAUNCH(true, true); else MIORI_TMA_LAUNCH(true, false);
+    } else {
+        if (sharded) MIORI_TMA_LAUNCH(false, true); else MIORI_TMA_LAUNCH(false, false);
+    }
 #undef MIORI_TMA_LAUNCH
     if (e != cudaSuccess) return cuda_fail(e, "gemv_tma launch");
     return MIORI_OK;
@@ -573,13 +612,14 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
 // Try the TMA path; returns 1 if this problem is not eligible (nothing launched).
 template <int BITS>
 int try_launch(const void* q, const void* s, const void* b, const void* x, void* y, uint32_t N,
-               uint32_t K, uint32_t M, uint32_t group, uint32_t flags, cudaStream_t stream) {
+               uint32_t K, uint32_t M, uint32_t group, uint32_t flags, cudaStream_t stream,
+               const Shard& sh = Shard()) {
     Plan pl;
 #define MIORI_TMA_TRY(EX, NTV)                                                                   \
     do {                                                                                         \
         pl = plan_stages<BITS, EX, NTV>(N, K, group);                                            \
         if (pl.ngrp == 0) return 1;                                                              \
-        return launch_one<BITS, EX, NTV>(pl, q, s, b, x, y, N, K, M, group, flags, stream);      \
+        return launch_one<BITS, EX, NTV>(pl, q, s, b, x, y, N, K, M, group, flags, stream, sh);  \
     } while (0)
     if (M <= 2) MIORI_TMA_TRY(true, 1);
     if (M <= 4) MIORI_TMA_TRY(true, 2);

@@ -4,3 +4,4 @@
 #include "backend.cu"
 #include "ops_api.cu"
 #include "gemm_tcgen05.cu"
+#include "peers.cu"
