@@ -174,6 +174,20 @@ size_t miori_gemm_static_scratch_bytes(void);
 int miori_gemm_bf16_cache_static(const void* A, const void* cache, void* C, uint32_t M, uint32_t N,
                                  uint32_t K, uint32_t flags, void* stream);
 
+/* ---- strided bf16 GEMM: replaces gemm_naive (shaders/ops.metal:199-251, bound by
+ *      src/ops.cpp:89-106), which carries the N=16 gate projection on every GEMM path
+ *      (src/engine.cpp:516, src/batch.cpp:237,435) and the wide-batch LM head against the bf16
+ *      embedding (src/batch.cpp:741). ------------------------------------------------------------ */
+
+/* C[M][N] (fp32, or bf16 with MIORI_OUT_BF16; rows ldc elements apart) = A[M][K] (bf16, rows lda
+ * apart) x B[N][K]^T (bf16, rows ldb apart), fp32 accumulation; any M, N, K >= 1.  Byte offsets
+ * of the reference's signature are folded into the pointers.  Operands whose bases and row
+ * pitches are 16-byte multiples (lda % 8 == 0, ldb % 8 == 0, ldc * element size % 16 == 0) run on
+ * the tcgen05 kernels of miori_gemm_bf16_cache; anything else runs on a plain fp32-FMA kernel. */
+int miori_gemm_bf16_strided(const void* A, uint32_t lda, const void* B, uint32_t ldb, void* C,
+                            uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, uint32_t flags,
+                            void* stream);
+
 /* ---- projection dispatch: replaces BatchEngine::linear / linear_p and Engine::p_gemm
  *      (reference src/batch.cpp:223-230, 429-431, src/engine.cpp:508-518), which route a
  *      projection to gemv4_b for narrow batches and to the bf16-cache GEMM otherwise. ------ */

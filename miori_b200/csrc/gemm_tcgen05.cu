@@ -193,7 +193,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // split-K: work item t covers k-blocks [kb0, kb1) of output tile t / splits and writes its
     // fp32 partial to slice t % splits of the workspace (splits == 1: straight to C)
     const uint32_t tiles = m_blocks * n_blocks * splits;
-    const uint32_t k_blocks = K / BK;
+    const uint32_t k_blocks = (K + BK - 1) / BK;  // TMA zero-fills a ragged last block
 
     pdl_launch_dependents();
 
@@ -419,7 +419,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t m_blocks = (M + 2 * BM - 1) / (2 * BM), n_blocks = (N + BN - 1) / BN;
     const uint32_t tiles = m_blocks * n_blocks * splits;
-    const uint32_t k_blocks = K / BK;
+    const uint32_t k_blocks = (K + BK - 1) / BK;  // TMA zero-fills a ragged last block
 
     pdl_launch_dependents();
 
@@ -586,37 +586,43 @@ splitk_reduce_kernel(const float4* __restrict__ ws, void* __restrict__ Cout, siz
     }
 }
 
-// [rows][K] bf16 row-major, box = [box_rows][64], 128-byte swizzle, zero fill out of range.
+// Row pitches in elements (0: dense).
+struct Ld {
+    uint32_t a = 0, b = 0, c = 0;
+};
+
+// [rows][K] bf16 row-major (rows `pitch` elements apart, 0: dense), box = [box_rows][64],
+// 128-byte swizzle, zero fill out of range.
 static int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
-                     uint32_t box_rows) {
+                     uint32_t box_rows, uint32_t pitch) {
     return make_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, rows, BK, box_rows,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
+                        CU_TENSOR_MAP_SWIZZLE_128B, pitch);
 }
 
 // Tensor map the epilogue stores through: C itself ([1][M][N], fp32 or bf16), or the split-K
 // workspace ([splits][M][N] fp32).  Boxes are 32 rows x 128 bytes with the 128-byte swizzle.
 static int make_tmap_out(CUtensorMap* map, void* Cm, float* ws, uint32_t M, uint32_t N,
-                         uint32_t splits, bool bf16) {
+                         uint32_t splits, bool bf16, uint32_t ldc) {
     if (splits > 1)
         return make_tmap_3d(map, ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, N, M, splits, 32, 32,
                             CU_TENSOR_MAP_SWIZZLE_128B);
     if (bf16)
         return make_tmap_3d(map, Cm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, 1, 64, 32,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
+                            CU_TENSOR_MAP_SWIZZLE_128B, ldc);
     return make_tmap_3d(map, Cm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, N, M, 1, 32, 32,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
+                        CU_TENSOR_MAP_SWIZZLE_128B, ldc);
 }
 
 // Launch the two-CTA kernel: clusters of 2, one pair per SM pair.
 static int launch_gemm_pair(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N,
                             uint32_t K, uint32_t flags, float* ws, uint32_t splits,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const Ld& ld) {
     CUtensorMap ta, tb, tc;
-    int rc = make_tmap(&ta, A, M, K, BM);
+    int rc = make_tmap(&ta, A, M, K, BM, ld.a);
     if (rc) return rc;
-    rc = make_tmap(&tb, Bc, N, K, pair::BN / 2);
+    rc = make_tmap(&tb, Bc, N, K, pair::BN / 2, ld.b);
     if (rc) return rc;
-    rc = make_tmap_out(&tc, Cm, ws, M, N, splits, (flags & MIORI_OUT_BF16) != 0);
+    rc = make_tmap_out(&tc, Cm, ws, M, N, splits, (flags & MIORI_OUT_BF16) != 0, ld.c);
     if (rc) return rc;
     const uint32_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + pair::BN - 1) / pair::BN) * splits;
     uint32_t pairs = (uint32_t)sm_count() / 2;
@@ -669,14 +675,14 @@ static int launch_reduce(void* Cm, uint32_t M, uint32_t N, uint32_t flags, float
 
 template <int BN>
 static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint32_t N, uint32_t K,
-                       uint32_t flags, float* ws, uint32_t splits, cudaStream_t stream) {
+                       uint32_t flags, float* ws, uint32_t splits, cudaStream_t stream, const Ld& ld) {
     using C = Cfg<BN>;
     CUtensorMap ta, tb, tc;
-    int rc = make_tmap(&ta, A, M, K, BM);
+    int rc = make_tmap(&ta, A, M, K, BM, ld.a);
     if (rc) return rc;
-    rc = make_tmap(&tb, Bc, N, K, BN);
+    rc = make_tmap(&tb, Bc, N, K, BN, ld.b);
     if (rc) return rc;
-    rc = make_tmap_out(&tc, Cm, ws, M, N, splits, (flags & MIORI_OUT_BF16) != 0);
+    rc = make_tmap_out(&tc, Cm, ws, M, N, splits, (flags & MIORI_OUT_BF16) != 0, ld.c);
     if (rc) return rc;
     const uint32_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     uint32_t grid = (uint32_t)sm_count();
@@ -733,7 +739,7 @@ struct GemmPlan {
 // idle and K is long enough to pay for the reduction, never below 4 k-blocks per split.
 static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, size_t ws_bytes) {
     const uint32_t sms = (uint32_t)sm_count();
-    const uint32_t k_blocks = K / BK;
+    const uint32_t k_blocks = (K + BK - 1) / BK;
     const size_t mn = (size_t)M * N;
     struct Shape {
         bool wide, pair, allowed;
@@ -773,14 +779,57 @@ static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, si
 }
 
 static int run_plan(const GemmPlan& p, const void* A, const void* cache, void* Cm, uint32_t M,
-                    uint32_t N, uint32_t K, uint32_t flags, float* ws, cudaStream_t stream) {
+                    uint32_t N, uint32_t K, uint32_t flags, float* ws, cudaStream_t stream,
+                    const Ld& ld = Ld()) {
     if (p.pair) {
-        int rc = launch_gemm_pair(A, cache, Cm, M, N, K, flags, ws, p.splits, stream);
+        int rc = launch_gemm_pair(A, cache, Cm, M, N, K, flags, ws, p.splits, stream, ld);
         if (rc == MIORI_OK && p.splits > 1) rc = launch_reduce(Cm, M, N, flags, ws, p.splits, stream);
         return rc;
     }
-    if (p.wide) return launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, p.splits, stream);
-    return launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, p.splits, stream);
+    if (p.wide) return launch_gemm<256>(A, cache, Cm, M, N, K, flags, ws, p.splits, stream, ld);
+    return launch_gemm<128>(A, cache, Cm, M, N, K, flags, ws, p.splits, stream, ld);
+}
+
+// Any-stride, any-alignment bf16 GEMM with fp32 accumulation: 32 x 32 output tile per CTA,
+// K in steps of 32 through shared memory.  Only for operands the TMA path cannot describe.
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(256)
+gemm_bf16_simt_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ B,
+                      void* __restrict__ Cout, uint32_t M, uint32_t N, uint32_t K, uint32_t lda,
+                      uint32_t ldb, uint32_t ldc) {
+    __shared__ float As[32][33], Bs[32][33];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // ty 0..7
+    const uint32_t m0 = blockIdx.y * 32u, n0 = blockIdx.x * 32u;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // rows ty, ty+8, ty+16, ty+24 of the tile; column tx
+    for (uint32_t k0 = 0; k0 < K; k0 += 32u) {
+#pragma unroll
+        for (uint32_t r = 0; r < 4u; ++r) {
+            const uint32_t row = ty + 8u * r, k = k0 + tx;
+            const uint32_t m = m0 + row, n = n0 + row;
+            As[row][tx] = (m < M && k < K) ? bf16_bits_to_float(A[(size_t)m * lda + k]) : 0.0f;
+            Bs[row][tx] = (n < N && k < K) ? bf16_bits_to_float(B[(size_t)n * ldb + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (uint32_t kk = 0; kk < 32u; ++kk) {
+            const float b = Bs[tx][kk];
+#pragma unroll
+            for (uint32_t r = 0; r < 4u; ++r) acc[r] = __fmaf_rn(As[ty + 8u * r][kk], b, acc[r]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+        const uint32_t m = m0 + ty + 8u * r, n = n0 + tx;
+        if (m < M && n < N) {
+            if (OUT_BF16)
+                reinterpret_cast<uint16_t*>(Cout)[(size_t)m * ldc + n] = (uint16_t)float_to_bf16_bits(acc[r]);
+            else
+                reinterpret_cast<float*>(Cout)[(size_t)m * ldc + n] = acc[r];
+        }
+    }
 }
 
 }  // namespace gemm
@@ -803,6 +852,53 @@ MIORI_API int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* C
 MIORI_API int miori_gemm_bf16_cache(const void* A, const void* cache, void* Cm, uint32_t M,
                                     uint32_t N, uint32_t K, uint32_t flags, void* stream) {
     return miori_gemm_bf16_cache_ws(A, cache, Cm, M, N, K, flags, nullptr, 0, stream);
+}
+
+MIORI_API int miori_gemm_bf16_strided(const void* A, uint32_t lda, const void* B, uint32_t ldb, void* Cm,
+                                      uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, uint32_t flags,
+                                      void* stream) {
+    const char* op = "miori_gemm_bf16_strided";
+    if (!A || !B || !Cm) return fail(MIORI_E_INVALID, "%s: null pointer", op);
+    if (M == 0 || N == 0 || K == 0)
+        return fail(MIORI_E_INVALID, "%s: empty shape M=%u N=%u K=%u", op, M, N, K);
+    if (lda < K || ldb < K || ldc < N)
+        return fail(MIORI_E_INVALID, "%s: a row pitch is shorter than its row (lda=%u ldb=%u K=%u ldc=%u N=%u)",
+                    op, lda, ldb, K, ldc, N);
+    const bool bf16 = (flags & MIORI_OUT_BF16) != 0, pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    const uint32_t csz = bf16 ? 2 : 4;
+    // what the TMA descriptors can express: 16-byte aligned bases and row pitches
+    const bool tma_ok = aligned16(A) && aligned16(B) && aligned16(Cm) && lda % 8 == 0 && ldb % 8 == 0 &&
+                        ((size_t)ldc * csz) % 16 == 0;
+    // TMA stores clip at 16-byte granularity, so the tensor-core kernels take the columns up to
+    // the last multiple of 16 bytes and the plain kernel the few that remain
+    uint32_t n_done = 0;
+    if (tma_ok) {
+        const uint32_t n_main = N - N % (16u / csz);
+        if (n_main) {
+            const gemm::GemmPlan p = gemm::plan_gemm(M, n_main, K, flags, 0);
+            gemm::Ld ld;
+            ld.a = lda;
+            ld.b = ldb;
+            ld.c = ldc;
+            const int rc = gemm::run_plan(p, A, B, Cm, M, n_main, K, flags, nullptr, (cudaStream_t)stream, ld);
+            if (rc) return rc;
+        }
+        n_done = n_main;
+    }
+    if (n_done == N) return MIORI_OK;
+    const uint16_t* Bp = static_cast<const uint16_t*>(B) + (size_t)n_done * ldb;
+    void* Cp = static_cast<uint8_t*>(Cm) + (size_t)n_done * csz;
+    const uint32_t n_rest = N - n_done;
+    const dim3 grid((n_rest + 31) / 32, (M + 31) / 32);
+    cudaError_t e;
+    if (bf16)
+        e = launch(gemm::gemm_bf16_simt_kernel<true>, grid, dim3(256), 0, (cudaStream_t)stream, pdl,
+                   static_cast<const uint16_t*>(A), Bp, Cp, M, n_rest, K, lda, ldb, ldc);
+    else
+        e = launch(gemm::gemm_bf16_simt_kernel<false>, grid, dim3(256), 0, (cudaStream_t)stream, pdl,
+                   static_cast<const uint16_t*>(A), Bp, Cp, M, n_rest, K, lda, ldb, ldc);
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_simt launch");
+    return MIORI_OK;
 }
 
 // ---- split-K GEMM on built-in scratch ------------------------------------------------------

@@ -25,15 +25,15 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // Row-major 2-D tensor [rows][inner] of `dtype` elements (`esize` bytes each), box
-// [box_rows][box_inner], zero fill outside the tensor.  The row pitch inner*esize must be a
-// multiple of 16 bytes and the base 16-byte aligned.
+// [box_rows][box_inner], zero fill outside the tensor.  Rows are row_pitch_elems apart (0: dense).
+// The row pitch in bytes must be a multiple of 16 and the base 16-byte aligned.
 inline int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
                         uint32_t esize, uint64_t inner, uint64_t rows, uint32_t box_inner,
-                        uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+                        uint32_t box_rows, CUtensorMapSwizzle swizzle, uint64_t row_pitch_elems = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
     const cuuint64_t dims[2] = {inner, rows};
-    const cuuint64_t strides[1] = {inner * esize};
+    const cuuint64_t strides[1] = {(row_pitch_elems ? row_pitch_elems : inner) * esize};
     const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -43,16 +43,17 @@ inline int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType 
     return MIORI_OK;
 }
 
-// Row-major 3-D tensor [d2][d1][d0] (d0 innermost), box [1][box1][box0], no fill (used for
-// stores, which clip at the tensor's edges).  d0*esize and d1*d0*esize must be multiples of 16
-// bytes and the base 16-byte aligned.
+// Row-major 3-D tensor [d2][d1][d0] (d0 innermost, rows row_pitch_elems apart, 0: dense), box
+// [1][box1][box0], no fill (used for stores, which clip at the tensor's edges).  The row pitch and
+// the slice pitch in bytes must be multiples of 16 and the base 16-byte aligned.
 inline int make_tmap_3d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
                         uint32_t esize, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box0,
-                        uint32_t box1, CUtensorMapSwizzle swizzle) {
+                        uint32_t box1, CUtensorMapSwizzle swizzle, uint64_t row_pitch_elems = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(MIORI_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+    const uint64_t pitch = row_pitch_elems ? row_pitch_elems : d0;
     const cuuint64_t dims[3] = {d0, d1, d2};
-    const cuuint64_t strides[2] = {d0 * esize, d0 * d1 * esize};
+    const cuuint64_t strides[2] = {pitch * esize, pitch * d1 * esize};
     const cuuint32_t box[3] = {box0, box1, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,

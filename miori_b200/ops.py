@@ -98,6 +98,26 @@ def gemm_bf16_cache(A, cache, N, flags=0, out=None, workspace=None):
     return Cm
 
 
+def gemm_bf16_strided(A, B, flags=0, out=None):
+    """C[M][N] = A[M][K] x B[N][K]^T for bf16 operands whose rows may be strided (views of
+    larger tensors, last dimension contiguous); `out` may be a strided view too."""
+    if not (A.is_cuda and B.is_cuda):
+        raise ValueError("miori_b200 ops need CUDA tensors (there is no CPU path)")
+    if A.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
+        raise TypeError("gemm_bf16_strided: bf16 operands expected")
+    M, K = A.shape
+    N = B.shape[0]
+    if B.shape[1] != K or A.stride(1) != 1 or B.stride(1) != 1:
+        raise ValueError("gemm_bf16_strided: A [M][K] and B [N][K] with contiguous rows expected")
+    dt = torch.bfloat16 if flags & OUT_BF16 else torch.float32
+    Cm = out if out is not None else torch.empty((M, N), dtype=dt, device=A.device)
+    if Cm.dtype != dt or Cm.shape != (M, N) or Cm.stride(1) != 1:
+        raise ValueError("gemm_bf16_strided: bad output tensor")
+    check(lib.miori_gemm_bf16_strided(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0),
+                                      Cm.data_ptr(), Cm.stride(0), M, N, K, flags, _stream()))
+    return Cm
+
+
 def linear4(q, s, b, cache, x, group=32, flags=0, out=None, workspace=None):
     """Projection dispatch (packed-weight GEMV for M <= 8, and M <= 16 while K <= 2048; bf16-cache
     GEMM above)."""

@@ -62,6 +62,11 @@ void gemv8_b_off(Metal& m, MTL::ComputeCommandEncoder* e, const Weights& w, cons
 // reference src/ops.h:203-205 -- row-major bf16 [N][K] from 8-bit weights
 void dequant8(Metal& m, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q,
               const Tensor& s, const Tensor& b, MTL::Buffer* out, uint32_t N, uint32_t K);
+// reference src/ops.h:30-33 -- C[M][N] (f32) = A[M][K] (bf16) x B[N][K]^T (bf16), row pitches in
+// elements, byte offsets into the three buffers
+void gemm_naive(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
+                MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t lda, uint32_t ldb,
+                uint32_t ldc, uint32_t aoff = 0, uint32_t boff = 0, uint32_t coff = 0);
 // reference src/ops.h:207-209 -- the small-M tile shape; same kernel, same result per row
 void gemm_mpp32(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
                 MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t boff = 0);

@@ -213,6 +213,14 @@ void gemm_mpp(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buff
     gemm_mpp_off(m, e, A, B, C, M, N, K, 0, boff, 0);
 }
 
+void gemm_naive(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
+                MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t lda, uint32_t ldb,
+                uint32_t ldc, uint32_t aoff, uint32_t boff, uint32_t coff) {
+    check(miori_gemm_bf16_strided(at(A, aoff), lda, at(B, boff), ldb, at_mut(C, coff), ldc, M, N, K,
+                                  MIORI_OUT_F32, e->stream()),
+          "gemm_naive");
+}
+
 void gemm_mpp32(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
                 MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t boff) {
     gemm_mpp_off(m, e, A, B, C, M, N, K, 0, boff, 0);

@@ -144,3 +144,60 @@ def test_linear_dispatch(port, M):
     assert_close(y_nocache.cpu().numpy(), want, what=f"linear4 (no cache) M={M}")
     if M <= 16:
         assert torch.equal(y, miori_b200.gemv4(q, s, b, x, group=64))
+
+
+# ---- strided bf16 GEMM (the reference's gemm_naive, shaders/ops.metal:199-251) ---------------
+
+def _bf16_randn(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g).to(torch.bfloat16).to(DEV)
+
+
+@pytest.mark.parametrize("M,N,K,lda,ldb,ldc,why", [
+    (64, 16, 2048, 2048, 2048, 16, "gate projection: N=16 against the bf16 weights"),
+    (23, 16, 2048, 4096, 2048, 16, "gate on a slice of a wider activation buffer"),
+    (32, 4096, 2048, 2048, 2048, 4096, "wide-batch head against a bf16 table"),
+    (200, 130, 128, 2048, 128, 136, "attention scores: K=128, ragged M and N, padded C rows"),
+    (130, 128, 200, 200, 4096, 2048, "probabilities x V: K not a multiple of 64"),
+    (300, 72, 96, 104, 96, 72, "small everything, K below one block"),
+])
+def test_strided_gemm_tma_path(port, M, N, K, lda, ldb, ldc, why):
+    """Row pitches that are multiples of 16 bytes run on the tcgen05 kernels; compared with the
+    oracle GEMM on dense copies, and the padding of C must stay untouched."""
+    Abig, Bbig = _bf16_randn((M, lda), 1 + M), _bf16_randn((N, ldb), 2 + N)
+    A, B = Abig[:, :K], Bbig[:, :K]
+    Cbig = torch.full((M, ldc), -7.0, device=DEV)
+    miori_b200.gemm_bf16_strided(A, B, out=Cbig[:, :N])
+    torch.cuda.synchronize()
+    want = port.gemm_bf16(u16(A.contiguous()), u16(B.contiguous()))
+    assert_close(Cbig[:, :N].cpu().numpy(), want, rel_max=1e-4, what=why)
+    assert bool((Cbig[:, N:] == -7.0).all())
+    assert miori_b200.lib.miori_device_error_poll() == 0
+
+
+@pytest.mark.parametrize("M,N,K,lda,ldb,ldc", [(37, 50, 70, 77, 71, 53), (5, 3, 129, 131, 133, 3)])
+def test_strided_gemm_odd_pitches(port, M, N, K, lda, ldb, ldc):
+    """Pitches and sizes TMA cannot describe take the plain kernel; same contract."""
+    Abig, Bbig = _bf16_randn((M, lda), 3), _bf16_randn((N, ldb), 4)
+    A, B = Abig[:, :K], Bbig[:, :K]
+    Cbig = torch.full((M, ldc), 9.0, device=DEV)
+    miori_b200.gemm_bf16_strided(A, B, out=Cbig[:, :N])
+    c16 = miori_b200.gemm_bf16_strided(A, B, flags=miori_b200.OUT_BF16)
+    torch.cuda.synchronize()
+    want = port.gemm_bf16(u16(A.contiguous()), u16(B.contiguous()))
+    assert_close(Cbig[:, :N].cpu().numpy(), want, rel_max=1e-4, what="odd pitches")
+    assert bool((Cbig[:, N:] == 9.0).all())
+    assert torch.equal(c16, Cbig[:, :N].to(torch.bfloat16))
+
+
+def test_strided_gemm_equals_cache_gemm_and_rejects_bad_pitch():
+    """On a dense cache the strided entry is the cache GEMM, bit for bit."""
+    N, K = 3072, 2048
+    _, _, _, cache = _weights(N, K, 64, seed=77)
+    A = synth.make_activation(48, K, seed=9, device=DEV)
+    got = miori_b200.gemm_bf16_strided(A, cache.view(N, K))
+    assert torch.equal(got, miori_b200.gemm_bf16_cache(A, cache, N))
+    with pytest.raises(miori_b200.MioriError):
+        check = miori_b200.check
+        check(miori_b200.lib.miori_gemm_bf16_strided(A.data_ptr(), K - 8, cache.data_ptr(), K,
+                                                     got.data_ptr(), N, 48, N, K, 0, None))
