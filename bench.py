@@ -244,8 +244,29 @@ def main():
     bytes_pass = layers * sum(packed_bytes(N, K, 4, G) for N, K in SHAPES)  # whole job
     say("weights ready")
     MMAX = max(M_SWEEP)
-    x_dev = {M: [synth.make_activation(M, K, seed=50 + M, device=dev) for _, K in SHAPES] for M in M_SWEEP}
-    y_loc = {M: [torch.empty((M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
+    # the four activations of a pass live in one device buffer, and so do its four outputs, so the
+    # end-to-end leg moves each pass's inputs and results with one copy each way
+    def carve(flat, shapes):
+        out, at = [], 0
+        for shp in shapes:
+            n = shp[0] * shp[1]
+            n_al = (n + 127) // 128 * 128  # keep every view 256-byte aligned
+            out.append(flat[at:at + n].view(shp))
+            at += n_al
+        return out
+
+    def flat_len(shapes):
+        return sum((a * b + 127) // 128 * 128 for a, b in shapes)
+
+    x_flat, y_flat, x_dev, y_loc = {}, {}, {}, {}
+    for M in M_SWEEP:
+        xs = [(M, K) for _, K in SHAPES]
+        ys = [(M, N // world) for N, _ in SHAPES]
+        x_flat[M] = torch.empty(flat_len(xs), dtype=torch.bfloat16, device=dev)
+        y_flat[M] = torch.empty(flat_len(ys), dtype=torch.float32, device=dev)
+        x_dev[M], y_loc[M] = carve(x_flat[M], xs), carve(y_flat[M], ys)
+        for v, (_, K) in zip(x_dev[M], SHAPES):
+            v.copy_(synth.make_activation(M, K, seed=50 + M, device=dev))
     # N > 1: the gathered outputs.  "peer": y[M][N] at the same offset of every rank's arena,
     # written by all ranks' GEMV epilogues over NVLink; "nccl": rank-major blocks from ncclAllGather
     grp, y_off, gather = None, None, "none"
@@ -396,22 +417,35 @@ def main():
     # ---- e2e: host buffers through the C ABI, copies inside the timed region
     stream = torch.cuda.current_stream().cuda_stream
     h2d = d2h = 0
-    host_x, host_y = {}, {}
+    host_x, host_y, dev_y = {}, {}, {}
     for M in M_SWEEP:
-        host_x[M] = [x.cpu().pin_memory() for x in x_dev[M]]
-        host_y[M] = [torch.empty((world * M, N // world)).pin_memory() if world > 1 and grp is None
-                     else torch.empty((M, N)).pin_memory() for N, _ in SHAPES]
-        h2d += sum(t.numel() * 2 for t in host_x[M])
-        d2h += sum(t.numel() * 4 for t in host_y[M])
+        host_x[M] = x_flat[M].cpu().pin_memory()
+        if world > 1 and grp is not None:   # gathered outputs: consecutive blocks of the arena
+            lo, hi = y_off[M][0], y_off[M][-1] + M * SHAPES[-1][0] * 4
+            dev_y[M] = grp.tensor(lo, ((hi - lo) // 4,))
+        elif world > 1:                      # NCCL: four separate gathered tensors
+            dev_y[M] = None
+        else:
+            dev_y[M] = y_flat[M]
+        if dev_y[M] is not None:
+            host_y[M] = torch.empty(dev_y[M].numel()).pin_memory()
+            d2h += dev_y[M].numel() * 4
+        else:
+            host_y[M] = [torch.empty((world * M, N // world)).pin_memory() for N, _ in SHAPES]
+            d2h += sum(t.numel() * 4 for t in host_y[M])
+        h2d += host_x[M].numel() * 2
 
     def e2e_step():
         for M in M_SWEEP:
-            for hx, dx in zip(host_x[M], x_dev[M]):
-                check(lib.miori_memcpy_h2d(dx.data_ptr(), hx.data_ptr(), hx.numel() * 2, stream))
+            check(lib.miori_memcpy_h2d(x_flat[M].data_ptr(), host_x[M].data_ptr(),
+                                       host_x[M].numel() * 2, stream))
             graphs[M].replay()
-            srcs = y_all[M] if world > 1 else y_loc[M]
-            for hy, dy in zip(host_y[M], srcs):
-                check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
+            if dev_y[M] is not None:
+                check(lib.miori_memcpy_d2h(host_y[M].data_ptr(), dev_y[M].data_ptr(),
+                                           host_y[M].numel() * 4, stream))
+            else:
+                for hy, dy in zip(host_y[M], y_all[M]):
+                    check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
             check(lib.miori_stream_sync(stream))  # the host consumes this pass's result
 
     say("per-M breakdown done")
