@@ -102,10 +102,12 @@ int miori_stream_sync(void* stream);
 
 /* y[m][n] = sum_k (code[n][k]*s[n][k/group] + b[n][k/group]) * x[m][k], 1 <= M <= 32.
  * The result of a row m does not depend on M (reference shaders/batch.metal:142-144)
- * within the same numeric path: M <= 4 dequantizes in fp32 (as gemv4 / gemv4_b do);
- * M > 4 multiplies bf16-rounded weights on the tensor cores (as the reference does
- * for wide batches through its bf16 cache, src/batch.cpp:223-230) unless
- * MIORI_GEMV_EXACT is set.  Requires K % group == 0, group in {32,64}; q,s,b,x 16-byte
+ * within the same numeric path: M <= 4 dequantizes in fp32 (as gemv4 / gemv4_b do; at
+ * group 64 the 4-bit kernel sums a group's two halves in a different order for M = 3, 4
+ * than for M <= 2, so those agree to fp32 rounding rather than bit for bit, while group
+ * 32 is bit-identical for all M <= 4); M > 4 multiplies bf16-rounded weights on the
+ * tensor cores (as the reference does for wide batches through its bf16 cache,
+ * src/batch.cpp:223-230) unless MIORI_GEMV_EXACT is set.  Requires K % group == 0, group in {32,64}; q,s,b,x 16-byte
  * aligned.  Only M rows of x are read and M rows of y written (the reference's
  * gemv4_b always touches four, shaders/batch.metal:178-179). */
 int miori_gemv4(const void* q, const void* s, const void* b, const void* x, void* y,

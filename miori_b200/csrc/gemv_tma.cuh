@@ -76,8 +76,9 @@ __device__ __forceinline__ uint32_t x_unit(uint32_t step, uint32_t t, uint32_t w
 }
 
 // Stage x for the MMA B operand: permuted to the k order of the A fragments (plus 16*x for
-// 8-bit codes), laid out by x_unit(); for EXACT also the fp32 sum of x over every chunk.
-template <int BITS, bool EXACT, int MP>
+// 8-bit codes), laid out by x_unit(); for EXACT also the fp32 sum of x over every chunk (PAIR:
+// over every pair of chunks, i.e. every 64-weight group).
+template <int BITS, bool EXACT, int MP, bool PAIR>
 __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, uint4* xs,
                                                float* xsum, uint32_t M, uint32_t K,
                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
@@ -112,9 +113,11 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
             const uint32_t m = i / cpr, c = i - m * cpr;
             float sum = 0.0f;
             if (m < M && c < chunks) {
-                const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c * CW);
+                // PAIR: both chunks of a 64-weight group carry the sum over the whole group
+                const uint32_t c0 = PAIR ? (c & ~1u) : c;
+                const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c0 * CW);
 #pragma unroll
-                for (int j = 0; j < CW / 8; ++j) {
+                for (int j = 0; j < (PAIR ? 2 : 1) * CW / 8; ++j) {
                     const uint4 v = __ldg(xp + j);
                     sum += bf16lo(v.x); sum += bf16hi(v.x); sum += bf16lo(v.y); sum += bf16hi(v.y);
                     sum += bf16lo(v.z); sum += bf16hi(v.z); sum += bf16lo(v.w); sum += bf16hi(v.w);
@@ -128,7 +131,12 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
 // ROOMY: compiled for one CTA per SM (up to 120 registers instead of 56).  Problems of at most
 // two tiles per SM run 4-18 % faster that way (no spills, freer scheduling); long streams prefer
 // two CTAs per SM.
-template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY>
+// PAIR (4-bit, group 64, EXACT, NT = 1): the two 32-weight chunks of a scale group sit in
+// neighbouring lanes, so the MMA columns are (chunk pair, activation row) instead of (chunk,
+// row) and one column set serves four activation rows.  Used for M = 3, 4 at group 64; the sums
+// of a group's two chunks then meet inside the tensor core instead of after the scale, so a row
+// agrees with its M <= 2 value to fp32 rounding, not bit for bit.
+template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR>
 __global__ void __launch_bounds__(THREADS, (NT == 1 && !ROOMY) ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_s,
@@ -142,7 +150,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
     constexpr int SK = 4 * CW;              // k per step
     constexpr int KC = 16 * SK;             // k per slab: 16 steps, 4 per warp of a group
-    constexpr int MP = EXACT ? 2 * NT : 8 * NT;
+    static_assert(!PAIR || (EXACT && NT == 1 && BITS == 4), "PAIR is an EXACT 4-bit single-set mode");
+    constexpr int MP = EXACT ? (PAIR ? 4 : 2 * NT) : 8 * NT;
     constexpr float OFF = BITS == 4 ? 128.0f : 2176.0f;  // sum of the 128 offsets per code
     constexpr uint32_t MASK = 0x000F000Fu, MAGIC = 0x43004300u;  // bf16 128.0 in both halves
 
@@ -273,7 +282,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     };
 
-    stage_x_padded<BITS, EXACT, MP>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+    stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
@@ -290,14 +299,15 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     uint32_t xadv[NT];      // advance per k-slab (0 for masked lanes, which read zeros)
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-        const uint32_t m = EXACT ? (2u * j + (n & 1u)) : (8u * j + n);
-        const bool active = EXACT ? ((n >> 1) == t) : true;
+        const uint32_t m = PAIR ? (n & 3u) : EXACT ? (2u * j + (n & 1u)) : (8u * j + n);
+        const bool active = PAIR ? ((n >> 2) == (t >> 1)) : EXACT ? ((n >> 1) == t) : true;
         xb[j] = active ? smem_addr(xs + (size_t)m * pitch + x_unit(wg, t, 0)) : smem_addr(zeros);
         xadv[j] = active ? (uint32_t)SLAB_X_BYTES * kpar : 0u;  // groups sharing a tile stride kpar slabs
     }
     const uint32_t xs_adv = 256u * kpar;                            // chunk sums per k-slab stride (bytes)
-    uint32_t xsp = smem_addr(xsum) + lc0 * 4u;                      // chunk (ks*16 + i4*4 + wg)*4 + t of row 0
     const uint32_t xs_row = cpr * 4u;
+    // chunk (ks*16 + i4*4 + wg)*4 + t of row 0 (PAIR: of the lane's first row, 0 or 2)
+    uint32_t xsp = smem_addr(xsum) + lc0 * 4u + (PAIR ? (t & 1u) * 2u * xs_row : 0u);
     float* gred = red + (size_t)grp * Red<MP>::GROUP_FLOATS;
 
     float acc[NT][4];
@@ -398,7 +408,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                             const float xs0 = ldsf32(xsa + (2 * j) * xs_row);
                             acc[j][0] = __fmaf_rn(sc0, d0[j][0] + d1[j][0], __fmaf_rn(bt0, xs0, acc[j][0]));
                             acc[j][2] = __fmaf_rn(sc1, d0[j][2] + d1[j][2], __fmaf_rn(bt1, xs0, acc[j][2]));
-                            if (2u * j + 1u < M) {  // CTA-uniform: the odd activation row exists
+                            if (PAIR || 2u * j + 1u < M) {  // CTA-uniform: the odd activation row exists
                                 const float xs1 = ldsf32(xsa + (2 * j + 1) * xs_row);
                                 acc[j][1] = __fmaf_rn(sc0, d0[j][1] + d1[j][1], __fmaf_rn(bt0, xs1, acc[j][1]));
                                 acc[j][3] = __fmaf_rn(sc1, d0[j][3] + d1[j][3], __fmaf_rn(bt1, xs1, acc[j][3]));
@@ -436,7 +446,17 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         constexpr int WS = Red<MP>::WS;
         float* buf = gred + (size_t)(tile_it & 1u) * 4 * WS;
         float* mine = buf + (size_t)wg * WS;
-        if (EXACT) {
+        if (PAIR) {
+            // lanes t and t^2 hold the two chunk pairs of the same two activation rows
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[0][e] += __shfl_xor_sync(0xFFFFFFFFu, acc[0][e], 2);
+            if (t < 2u) {  // t = 0: rows 0, 1; t = 1: rows 2, 3
+                mine[g * MP + 2 * t] = acc[0][0];
+                mine[g * MP + 2 * t + 1] = acc[0][1];
+                mine[(g + 8) * MP + 2 * t] = acc[0][2];
+                mine[(g + 8) * MP + 2 * t + 1] = acc[0][3];
+            }
+        } else if (EXACT) {
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -509,10 +529,10 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
 }
 
-template <int BITS, bool EXACT, int NT>
+template <int BITS, bool EXACT, int NT, bool PAIR>
 size_t fixed_smem(uint32_t K) {
     constexpr int KC = 16 * 4 * (128 / BITS);
-    constexpr int MP = EXACT ? 2 * NT : 8 * NT;
+    constexpr int MP = EXACT ? (PAIR ? 4 : 2 * NT) : 8 * NT;
     const uint32_t kslabs = (K + KC - 1) / KC, steps_p = kslabs * 16;
     size_t bytes = (size_t)MP * (steps_p * STEP_UNITS + 1) * 16 + ZERO_BYTES;
     if (EXACT) bytes += (size_t)MP * steps_p * 4 * 4;
@@ -535,12 +555,12 @@ struct Plan {
     uint32_t grid, ngrp, nsg, kpar;
     bool roomy;  // one CTA per SM and few tiles: use the instantiation with the larger register budget
 };
-template <int BITS, bool EXACT, int NT>
+template <int BITS, bool EXACT, int NT, bool PAIR>
 Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
     constexpr int KC = 16 * 4 * (128 / BITS);
     Plan p = {0, 0, 0, 1, false};
     if ((K / group) % 8 != 0) return p;  // scale rows must have a 16-byte pitch for TMA
-    const size_t fixed = fixed_smem<BITS, EXACT, NT>(K);
+    const size_t fixed = fixed_smem<BITS, EXACT, NT, PAIR>(K);
     const uint32_t tiles = (N + 15) / 16, kslabs = (K + KC - 1) / KC;
     const uint32_t sms = (uint32_t)sm_count();
     // A CTA is sized for half an SM (shared memory and, for M <= 2 / 5..8, registers).  Short
@@ -568,12 +588,12 @@ Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
     return p;
 }
 
-template <int BITS, bool EXACT, int NT>
+template <int BITS, bool EXACT, int NT, bool PAIR>
 int launch_one(Plan plan, const void* q, const void* s, const void* b, const void* x, void* y,
                uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
                cudaStream_t stream, const Shard& sh) {
     constexpr int KC = 16 * 4 * (128 / BITS);
-    const size_t smem = fixed_smem<BITS, EXACT, NT>(K) + (size_t)plan.ngrp * plan.nsg * STAGE_BYTES;
+    const size_t smem = fixed_smem<BITS, EXACT, NT, PAIR>(K) + (size_t)plan.ngrp * plan.nsg * STAGE_BYTES;
     const uint32_t grid = plan.grid;
     const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
     const uint32_t gshift = group == 32 ? 5u : 6u;
@@ -593,8 +613,8 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     cudaError_t e;
 #define MIORI_TMA_LAUNCH(OB, SH)                                                                 \
     do {                                                                                         \
-        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1>                    \
-                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false>;                     \
+        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR>              \
+                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR>;               \
         e = cudaSuccess;                                                                         \
         if (smem > 48 * 1024)                                                                    \
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -622,20 +642,25 @@ int try_launch(const void* q, const void* s, const void* b, const void* x, void*
                uint32_t K, uint32_t M, uint32_t group, uint32_t flags, cudaStream_t stream,
                const Shard& sh = Shard()) {
     Plan pl;
-#define MIORI_TMA_TRY(EX, NTV)                                                                   \
+#define MIORI_TMA_TRY(EX, NTV, PR)                                                               \
     do {                                                                                         \
-        pl = plan_stages<BITS, EX, NTV>(N, K, group);                                            \
+        pl = plan_stages<BITS, EX, NTV, PR>(N, K, group);                                        \
         if (pl.ngrp == 0) return 1;                                                              \
-        return launch_one<BITS, EX, NTV>(pl, q, s, b, x, y, N, K, M, group, flags, stream, sh);  \
+        return launch_one<BITS, EX, NTV, PR>(pl, q, s, b, x, y, N, K, M, group, flags, stream, sh); \
     } while (0)
-    if (M <= 2) MIORI_TMA_TRY(true, 1);
-    if (M <= 4) MIORI_TMA_TRY(true, 2);
+    if (M <= 2) MIORI_TMA_TRY(true, 1, false);
+    if constexpr (BITS == 4) {
+        // three and four rows at group 64: one column set instead of two (13-21 % faster); one
+        // and two rows stay on the per-chunk columns, which stage half as much x
+        if (M <= 4 && group == 64) MIORI_TMA_TRY(true, 1, true);
+    }
+    if (M <= 4) MIORI_TMA_TRY(true, 2, false);
     if constexpr (BITS == 8) {
         return 1;
     } else {
-        if (M <= 8) MIORI_TMA_TRY(false, 1);
-        if (M <= 16) MIORI_TMA_TRY(false, 2);
-        MIORI_TMA_TRY(false, 4);
+        if (M <= 8) MIORI_TMA_TRY(false, 1, false);
+        if (M <= 16) MIORI_TMA_TRY(false, 2, false);
+        MIORI_TMA_TRY(false, 4, false);
     }
 #undef MIORI_TMA_TRY
 }

@@ -96,6 +96,23 @@ def test_rows_do_not_depend_on_m():
     assert np.array_equal(y5, y8[:5]), "rows differ between M=5 and M=8"
 
 
+def test_rows_at_group_64_agree_across_m(port):
+    """Group 64: M = 1, 2 share one arithmetic order and M = 3, 4 another (chunk-pair columns);
+    inside each pair rows are bit-identical, across them they agree to fp32 rounding."""
+    N, K = 528, 2048
+    q, s, b, x = _case(4, N, K, 4, 64, seed=91)
+    y4 = _run(4, q, s, b, x, 64)
+    y3 = _run(4, q, s, b, x[:3].contiguous(), 64)
+    y2 = _run(4, q, s, b, x[:2].contiguous(), 64)
+    y1 = _run(4, q, s, b, x[:1].contiguous(), 64)
+    assert np.array_equal(y3, y4[:3])
+    assert np.array_equal(y1, y2[:1])
+    assert closeness(y2, y4[:2])[0] < TOL_EXACT_PATH
+    want = port.gemv(4, u32(q), u16(s), u16(b), u16(x), 64)
+    assert_close(y4, want, rel_max=TOL_EXACT_PATH, what="pair columns M=4")
+    assert_close(y3, want[:3], rel_max=TOL_EXACT_PATH, what="pair columns M=3")
+
+
 @pytest.mark.parametrize("flags", [0x400, 0x800])
 @pytest.mark.parametrize("bits,M", [(4, 1), (4, 3), (4, 8), (4, 32), (8, 2)])
 def test_every_kernel_family_matches_oracle(port, bits, M, flags):
