@@ -173,8 +173,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, uint32_t splits, uint32_t M,
-                         uint32_t N, uint32_t K) {
+                         uint32_t N, uint32_t K, uint32_t a_box_rows) {
     using C = Cfg<BN>;
+    // Bytes one k-block delivers: the A box holds only a_box_rows rows when M is small (a box
+    // that reaches far past the tensor's last row is served slowly); the rest of the 128-row A
+    // region then keeps stale bytes, which only feed accumulator lanes nobody reads.
+    const uint32_t stage_tx = a_box_rows * BK * 2u + (uint32_t)C::B_BYTES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
@@ -239,7 +243,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const uint32_t kb0 = sp * k_blocks / splits, kb1 = (sp + 1u) * k_blocks / splits;
                 pre = min((uint32_t)C::STAGES, kb1 - kb0);
                 for (uint32_t i = 0; i < pre; ++i) {
-                    mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+                    mbar_expect_tx(full_bar(i), stage_tx);
                     tma_load_2d(tiles_base + i * C::STAGE_BYTES + C::A_BYTES, &tmap_b,
                                 (int)((kb0 + i) * BK), (int)(tc.n_blk * BN), full_bar(i));
                 }
@@ -254,7 +258,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const uint32_t sa = tiles_base + s * C::STAGE_BYTES;
                     if (it >= pre) {
                         if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, 1))) break;
-                        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                        mbar_expect_tx(full_bar(s), stage_tx);
                         tma_load_2d(sa + C::A_BYTES, &tmap_b, (int)(kb * BK), (int)(tc.n_blk * BN),
                                     full_bar(s));
                     }
@@ -678,7 +682,8 @@ static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint
                        uint32_t flags, float* ws, uint32_t splits, cudaStream_t stream, const Ld& ld) {
     using C = Cfg<BN>;
     CUtensorMap ta, tb, tc;
-    int rc = make_tmap(&ta, A, M, K, BM, ld.a);
+    const uint32_t a_box = M >= (uint32_t)BM ? (uint32_t)BM : (M + 7u) / 8u * 8u;
+    int rc = make_tmap(&ta, A, M, K, a_box, ld.a);
     if (rc) return rc;
     rc = make_tmap(&tb, Bc, N, K, BN, ld.b);
     if (rc) return rc;
@@ -694,13 +699,13 @@ static int launch_gemm(const void* A, const void* Bc, void* Cm, uint32_t M, uint
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e == cudaSuccess)
             e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
-                       tc, splits, M, N, K);
+                       tc, splits, M, N, K, a_box);
     } else {
         auto kern = gemm_bf16_tcgen05_kernel<BN, false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e == cudaSuccess)
             e = launch(kern, dim3(grid), dim3(THREADS), (size_t)C::SMEM_BYTES, stream, pdl, ta, tb,
-                       tc, splits, M, N, K);
+                       tc, splits, M, N, K, a_box);
     }
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05 launch");
     if (splits > 1) return launch_reduce(Cm, M, N, flags, ws, splits, stream);
