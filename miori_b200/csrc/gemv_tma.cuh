@@ -128,6 +128,56 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
     }
 }
 
+// The same staging in one pass, for rows short enough that every thread handles one or two
+// units (K <= 2048): a thread loads a unit, stores it permuted, and the 4 (PAIR: 8) lanes that hold
+// a chunk (a 64-weight group) add up its fp32 sum with shuffles, so x is read once and there is
+// one load latency instead of two.  Whole warps iterate (THREADS and the units per row are
+// multiples of 32 resp. 16, so lane groups never straddle a chunk).  For long rows the two-pass
+// version above is faster: its loads are independent across iterations.
+template <int BITS, bool EXACT, int MP, bool PAIR>
+__device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, uint4* xs,
+                                                float* xsum, uint32_t M, uint32_t K,
+                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
+    constexpr int KU = BITS == 4 ? 8 : 4;
+    const uint32_t upr = steps_p * 16u;  // logical units per row
+    const uint32_t total = (uint32_t)MP * upr, lane = threadIdx.x & 31u;
+    for (uint32_t i0 = threadIdx.x - lane; i0 < total; i0 += THREADS) {
+        const uint32_t i = i0 + lane;
+        const uint32_t m = i / upr, u = i - m * upr;
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        float sum = 0.0f;
+        if (i < total && m < M && u * KU < K) {
+            if (BITS == 4) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
+                o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0,x4)
+                o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1,x5)
+                o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
+                o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3,x7)
+                if (EXACT)
+                    sum = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
+                          ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
+            } else {
+                const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + (size_t)m * K) + u);
+                const uint32_t x02 = __byte_perm(v.x, v.y, 0x5410);  // (x0,x2)
+                const uint32_t x13 = __byte_perm(v.x, v.y, 0x7632);  // (x1,x3)
+                const uint32_t sixteen = 0x41804180u, zero = 0u;     // bf16 16.0 pair
+                o.x = x02;
+                o.y = gemvmma::bf16x2_fma(x02, sixteen, zero);
+                o.z = x13;
+                o.w = gemvmma::bf16x2_fma(x13, sixteen, zero);
+                if (EXACT) sum = (bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y));
+            }
+        }
+        if (i < total) xs[(size_t)m * pitch + x_unit(u >> 4, (u >> 2) & 3u, u & 3u)] = o;
+        if (EXACT) {
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+            if (PAIR) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+            if (i < total && (u & 3u) == 0u) xsum[m * cpr + (u >> 2)] = sum;
+        }
+    }
+}
+
 // ROOMY: compiled for one CTA per SM (up to 120 registers instead of 56).  Problems of at most
 // two tiles per SM run 4-18 % faster that way (no spills, freer scheduling); long streams prefer
 // two CTAs per SM.
@@ -282,7 +332,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     };
 
-    stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+    // one-pass staging where it measured faster: one slab of K, and either the roomy
+    // instantiation or at most two staged rows
+    if ((ROOMY || MP <= 2) && kslabs == 1u)
+        stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+    else
+        stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
