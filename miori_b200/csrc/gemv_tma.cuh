@@ -306,28 +306,25 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     pdl_wait_prior();  // x (and y) belong to the predecessor until here
 
     // N-sharded launch (pa.world > 1): this rank's rows [row0, row0 + N) of an n_total-row output
-    // go to every rank's copy of y (at y_off in each arena); peers.cuh has the three-counter
-    // protocol.  Everything it needs is re-read from the kernel parameters and the control block
-    // at the point of use, so the single-GPU path carries no extra registers through the loop.
-    // a template parameter rather than a run-time test: the single-GPU instantiation then
-    // compiles exactly as if the peer path did not exist (a run-time branch cost 3-16 %)
+    // go into its own y (at user offset y_off of its arena) and, as {value, launch number}
+    // packets, into every peer's inbox; before the CTA exits it collects its share of the peers'
+    // rows (peers.cuh).  The launch number is re-read from the control block at the point of
+    // use, so the single-GPU path carries no extra registers through the loop; SHARDED is a
+    // template parameter rather than a run-time test because the single-GPU instantiation then
+    // compiles exactly as if the peer path did not exist (a run-time branch cost 3-16 %).
     const uint32_t world = SHARDED ? pa.world : 0u;
-    if (world > 1u && blockIdx.x == 0 && threadIdx.x == 0) peer_announce_ready(pa, peer_epoch(pa));
-    // one output element: y[m][row0 + row] here and, when sharded, on every peer; `first` is
-    // true for the calling thread's first tile (it then waits for the peers' go-ahead)
-    auto store_out = [&](uint32_t m, uint32_t row, float v, bool first) {
+    // one output element: y[m][row0 + row]
+    auto store_out = [&](uint32_t m, uint32_t row, float v) {
         const size_t idx = (size_t)m * n_total + row0 + row;
-        if (world <= 1u) {
-            if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)float_to_bf16_bits(v);
-            else reinterpret_cast<float*>(y)[idx] = v;
-            return;
-        }
+        const uint32_t bits = OUT_BF16 ? float_to_bf16_bits(v) : __float_as_uint(v);
+        if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)bits;
+        else reinterpret_cast<uint32_t*>(y)[idx] = bits;
         if constexpr (SHARDED) {
-            if (first) peer_wait_ready(pa, peer_epoch(pa));
-            for (uint32_t p = 0; p < world; ++p) {
-                uint8_t* yp = peer_arena(pa, p) + y_off;
-                if (OUT_BF16) reinterpret_cast<uint16_t*>(yp)[idx] = (uint16_t)float_to_bf16_bits(v);
-                else reinterpret_cast<float*>(yp)[idx] = v;
+            if (world > 1u) {
+                const uint32_t e = peer_epoch(pa);
+                const size_t elem = y_off / (OUT_BF16 ? 2u : 4u) + idx;
+                for (uint32_t p = 0; p < world; ++p)
+                    if (p != pa.rank) peer_send(peer_slot(pa, peer_arena(pa, p), e, elem), bits, e);
             }
         }
     };
@@ -553,7 +550,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (kpar > 1u) {
                 if (w == 0) kred[((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP) + o] = v;
             } else if (w == 0 && m < M && row < N && ok) {
-                store_out(m, row, v, tile_it == 0u);
+                store_out(m, row, v);
             }
         }
         if (kpar > 1u) {
@@ -565,7 +562,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     float v = kr[o];
                     for (uint32_t j = 1; j < kpar; ++j) v += kr[(size_t)j * (16 * MP) + o];
                     const uint32_t r = o & 15u, m = o >> 4, row = tile * 16u + r;
-                    if (m < M && row < N && ok) store_out(m, row, v, tile_it == 0u);
+                    if (m < M && row < N && ok) store_out(m, row, v);
                 }
             }
         }
@@ -578,9 +575,14 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
     }
-    if (world > 1u) {  // every thread of the CTA gets here: no early exits above
-        __syncthreads();
-        if (threadIdx.x == 0) peer_finish(pa, peer_epoch(pa));
+    if constexpr (SHARDED) {
+        if (world > 1u) {  // every thread of the CTA gets here: no early exits above
+            const uint32_t e = peer_epoch(pa);
+            __syncthreads();
+            peer_collect<OUT_BF16>(pa, e, y_off, M, n_total, row0, N);
+            __syncthreads();
+            if (threadIdx.x == 0) peer_finish(pa, e);
+        }
     }
 }
 

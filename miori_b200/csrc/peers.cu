@@ -19,27 +19,37 @@ using namespace miori_b200;
 namespace miori_b200 {
 namespace peers {
 
-// Copy this rank's block of an output -- src[M][n_local] elements, row pitch src_pitch bytes --
-// into columns [row0, row0 + n_local) of y[M][n_total] in every rank's arena (its own included),
-// under the same ready/done protocol as the fused GEMV.  16-byte pieces; the block's width,
-// offset and the row pitches are multiples of 16 bytes.
+// Send this rank's block of an output -- src[M][n_local] elements, row pitch src_pitch bytes --
+// to columns [row0, row0 + n_local) of y[M][n_total] on every rank (a plain copy into its own
+// arena, packets into the peers' inboxes), then collect the peers' blocks: the protocol of the
+// fused GEMV (peers.cuh) as a kernel of its own.
+template <bool BF16>
 __global__ void __launch_bounds__(256)
 allgather_kernel(const PeerArgs pa, const uint8_t* __restrict__ src, uint32_t src_pitch, size_t y_off,
-                 uint32_t M, uint32_t row_bytes, uint32_t off_bytes, uint32_t len_bytes) {
+                 uint32_t M, uint32_t n_total, uint32_t row0, uint32_t n_local) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const uint32_t e = peer_epoch(pa);
-    if (blockIdx.x == 0 && threadIdx.x == 0) peer_announce_ready(pa, e);
-    if (threadIdx.x == 0) peer_wait_ready(pa, e);
-    __syncthreads();
-    const uint32_t units = len_bytes / 16u;  // 16-byte pieces per row of the block
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)M * units;
+    constexpr uint32_t ES = BF16 ? 2u : 4u;
+    uint8_t* y = pa.local + PEER_CTL_BYTES + y_off;
+    const size_t base = y_off / ES;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)M * n_local;
          i += (size_t)gridDim.x * blockDim.x) {
-        const size_t m = i / units, u = i - m * units;
-        const uint4 v = *reinterpret_cast<const uint4*>(src + m * src_pitch + u * 16u);
-        const size_t at = y_off + m * row_bytes + off_bytes + u * 16u;
-        for (uint32_t p = 0; p < pa.world; ++p) *reinterpret_cast<uint4*>(peer_arena(pa, p) + at) = v;
+        const size_t m = i / n_local, c = i - m * n_local;
+        const size_t idx = m * n_total + row0 + c;
+        uint32_t bits;
+        if (BF16) {
+            bits = *reinterpret_cast<const uint16_t*>(src + m * src_pitch + c * 2u);
+            reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)bits;
+        } else {
+            bits = *reinterpret_cast<const uint32_t*>(src + m * src_pitch + c * 4u);
+            reinterpret_cast<uint32_t*>(y)[idx] = bits;
+        }
+        for (uint32_t p = 0; p < pa.world; ++p)
+            if (p != pa.rank) peer_send(peer_slot(pa, peer_arena(pa, p), e, base + idx), bits, e);
     }
+    __syncthreads();
+    peer_collect<BF16>(pa, e, y_off, M, n_total, row0, n_local);
     __syncthreads();
     if (threadIdx.x == 0) peer_finish(pa, e);
 }
@@ -65,6 +75,7 @@ static PeerArgs peer_args(const miori_peers* g) {
     pa.local = g->mapped[g->rank];
     pa.world = (uint32_t)g->world;
     pa.rank = (uint32_t)g->rank;
+    pa.user_bytes = g->user_bytes;
     return pa;
 }
 
@@ -91,8 +102,8 @@ static int gemv_allgather(const char* op, miori_peers* g, const void* q, const v
     sh.pa = peer_args(g);
     sh.n_total = n_total;
     sh.row0 = row0;
-    sh.y_off = PEER_CTL_BYTES + y_offset;
-    void* y_local = g->mapped[g->rank] + sh.y_off;
+    sh.y_off = y_offset;
+    void* y_local = g->mapped[g->rank] + PEER_CTL_BYTES + y_offset;
     if (g->world <= 1) {  // no peers: an ordinary GEMV into the local arena
         sh.pa.world = 0;
         if (row0 != 0 || n_local != n_total)
@@ -125,8 +136,10 @@ MIORI_API int miori_peers_create(int rank, int world, size_t arena_bytes, miori_
     g->user_bytes = arena_bytes;
     g->connected = world == 1;
     void* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, PEER_CTL_BYTES + arena_bytes);
-    if (e == cudaSuccess) e = cudaMemset(p, 0, PEER_CTL_BYTES + arena_bytes);
+    // control block, user area, and two inboxes of 8-byte packets (PEER_INBOX_FACTOR x user each)
+    const size_t total = PEER_CTL_BYTES + arena_bytes * (1 + 2 * PEER_INBOX_FACTOR);
+    cudaError_t e = cudaMalloc(&p, total);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, total);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         if (p) cudaFree(p);
@@ -243,13 +256,18 @@ MIORI_API int miori_allgather(miori_peers* g, const void* src, size_t y_offset, 
         return fail(MIORI_E_INVALID, "miori_allgather: offsets and row blocks must be multiples of 16 bytes");
     if (y_offset + (size_t)M * row_bytes > g->user_bytes)
         return fail(MIORI_E_INVALID, "miori_allgather: y does not fit the arena");
-    const size_t pieces = (size_t)M * (len / 16);
-    const unsigned blocks = (unsigned)std::min<size_t>((pieces + 255) / 256, (size_t)sm_count());
-    const cudaError_t e =
-        launch(peers::allgather_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
-               (flags & MIORI_LAUNCH_PDL) != 0, peers::peer_args(g), static_cast<const uint8_t*>(src),
-               (uint32_t)len, PEER_CTL_BYTES + y_offset, M, (uint32_t)row_bytes, (uint32_t)off,
-               (uint32_t)len);
+    const size_t elems = (size_t)M * n_local;
+    const unsigned blocks = (unsigned)std::min<size_t>((elems + 255) / 256, (size_t)sm_count());
+    const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    cudaError_t e;
+    if (elem_bytes == 2)
+        e = launch(peers::allgather_kernel<true>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, pdl,
+                   peers::peer_args(g), static_cast<const uint8_t*>(src), (uint32_t)len, y_offset, M,
+                   n_total, row0, n_local);
+    else
+        e = launch(peers::allgather_kernel<false>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, pdl,
+                   peers::peer_args(g), static_cast<const uint8_t*>(src), (uint32_t)len, y_offset, M,
+                   n_total, row0, n_local);
     if (e != cudaSuccess) return cuda_fail(e, "miori_allgather launch");
     return MIORI_OK;
 }

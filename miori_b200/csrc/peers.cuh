@@ -1,106 +1,118 @@
-// Device side of the N-sharded GEMV's fused all-gather: every rank (one process per GPU) owns
-// an "arena" of device memory that all other ranks map through CUDA IPC, with the output
-// buffers at the same offsets on every rank.  A kernel writes its rows of y straight into every
-// rank's copy with plain peer stores over NVLink; three small counters per rank pair, kept in a
-// control block at the start of each arena, order those stores against the readers:
+// Device side of the N-sharded GEMV's fused all-gather.  Every rank (one process per GPU) owns
+// an "arena" of device memory that all other ranks map through CUDA IPC:
 //
-//   ready[from]  "rank `from` has reached launch e": everything it enqueued before (the readers
-//                of the previous y) is complete, so its copy of y may be overwritten
-//   done[from]   "rank `from` has finished writing its rows of launch e into this arena"
-//   epoch        launches completed on this rank; every rank runs the same launch sequence, so
-//                launch numbers agree without any host involvement (CUDA graphs replay them)
+//   [ control block 256 B | user area (outputs, same offsets on every rank) | inbox 0 | inbox 1 ]
 //
-// A kernel (1) announces ready(e) to every peer once its stream predecessors are complete,
-// (2) before its first remote store waits until every peer has announced ready(e), (3) after its
-// last CTA has stored, announces done(e) to every peer and waits for every peer's done(e), so
-// "kernel complete" on a rank means "its whole y is complete".  All waits are bounded: after
-// about a second they record a device error, mark the control block and give up, so a missing
-// peer costs time but never hangs the GPU.  Only plain loads and stores cross the link: no
-// multicast, no TMA from or to peer memory.
+// A kernel writes the rows it computed into its own copy of y and, for every peer, into that
+// peer's inbox as 8-byte packets {value bits, launch number} -- one plain store over NVLink per
+// element, which arrives whole, so the packet is its own "ready" flag and no fence, release or
+// counter crosses the link (a system-scope fence costs 1.5-3.5 us here; the first version of this
+// protocol spent one per CTA).  Before it exits, every CTA of the receiving kernel takes a slice of
+// the output, waits (bounded) until the packets of the rows its peers own carry this launch's
+// number, and copies the values into y.  When the kernel completes on a rank its whole y is
+// there, so anything that follows on the stream may read it.
+//
+// Launch numbers: every rank runs the same sequence of these kernels, so the per-rank count of
+// completed launches (kept in the control block, bumped by the last CTA with local atomics only)
+// agrees across ranks without the host, and CUDA graphs replay it.  Inboxes alternate with the
+// launch number's parity: a rank can be at most one launch ahead of a peer (its launch e+1
+// completes only after the peer's rows of e+1 arrived, which the peer sends after finishing e),
+// so a packet of launch e+1 never lands on a slot a peer still reads for launch e.
+// All waits are bounded (~1 s): on expiry the kernel records a device error, marks the control
+// block and stops waiting, so a missing peer costs time but never hangs the GPU.  Only plain
+// loads and stores touch peer memory: no multicast, no TMA.
 #pragma once
 #include "common.cuh"
 
 namespace miori_b200 {
 
 constexpr int MAX_PEERS = 8;
-constexpr size_t PEER_CTL_BYTES = 256;  // control block at the start of every arena
-enum : uint32_t { CTL_READY = 0, CTL_DONE = 8, CTL_COUNT = 16, CTL_EPOCH = 17, CTL_ERR = 18 };
-
-constexpr size_t PEER_TABLE_OFFSET = 128;  // MAX_PEERS arena pointers inside the control block
+constexpr size_t PEER_CTL_BYTES = 256;      // control block at the start of every arena
+constexpr size_t PEER_TABLE_OFFSET = 128;   // MAX_PEERS arena pointers inside the control block
+constexpr size_t PEER_INBOX_FACTOR = 4;     // one inbox = 4 x user bytes: 8-byte packets for 2-byte elements
+enum : uint32_t { CTL_COUNT = 16, CTL_EPOCH = 17, CTL_ERR = 18 };
 
 struct PeerArgs {          // by value in kernel parameters
     uint8_t* local;        // this rank's arena; its control block holds, at PEER_TABLE_OFFSET,
                            // every rank's arena as mapped in this process (entry [rank] = local)
     uint32_t world, rank;  // world <= 1: no peers, kernels behave as single-GPU kernels
+    size_t user_bytes;     // size of the user area (the inboxes follow it)
 };
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint8_t* peer_arena(const PeerArgs& pa, uint32_t p) {
     return reinterpret_cast<uint8_t* const*>(pa.local + PEER_TABLE_OFFSET)[p];
 }
-__device__ __forceinline__ uint32_t* peer_ctl(const PeerArgs& pa, uint32_t p) {
-    return reinterpret_cast<uint32_t*>(p == pa.rank ? pa.local : peer_arena(pa, p));
-}
-// Counters are written and polled with relaxed system-scope accesses; ordering comes from the
-// one system-scope fence each CTA executes after its data stores (below) and from kernel
-// boundaries.  On B200 over NVLink a system-scope fence or release costs 1.5-3.5 us whether or
-// not stores are outstanding, so the protocol spends exactly one per CTA, all in parallel.
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint32_t* peer_ctl(const PeerArgs& pa) {
+    return reinterpret_cast<uint32_t*>(pa.local);
 }
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// Bounded wait until *p has reached `want` (counters only grow; compared modulo 2^32).
-__device__ __forceinline__ bool peer_wait_ge(uint32_t* ctl_local, const uint32_t* p, uint32_t want,
-                                             uint32_t code) {
-    if ((int32_t)(ld_relaxed_sys(p) - want) >= 0) return true;
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// The launch number this kernel runs as.  Stable for the kernel's whole life: only the last CTA
+// advances it, after every CTA has finished.  Call after the dependency wait.
+__device__ __forceinline__ uint32_t peer_epoch(const PeerArgs& pa) {
+    return ld_relaxed_sys(peer_ctl(pa) + CTL_EPOCH) + 1u;
+}
+// Packet slot of output element `elem` (index into the user area in units of the output's element
+// size, i.e. y_off / esize + m * n_total + row) in the inbox of launch e inside `arena`.
+__device__ __forceinline__ uint2* peer_slot(const PeerArgs& pa, uint8_t* arena, uint32_t e, size_t elem) {
+    uint8_t* inbox = arena + PEER_CTL_BYTES + pa.user_bytes * (1u + (e & 1u) * PEER_INBOX_FACTOR);
+    return reinterpret_cast<uint2*>(inbox) + elem;
+}
+// One element to one peer: value bits and launch number in a single 8-byte store.
+__device__ __forceinline__ void peer_send(uint2* slot, uint32_t bits, uint32_t e) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot), "r"(bits), "r"(e) : "memory");
+}
+// Bounded wait for the packet of launch e in a local slot; false if it never came.
+__device__ __forceinline__ bool peer_recv(const PeerArgs& pa, const uint2* slot, uint32_t e, uint32_t& bits) {
+    uint32_t got;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(got) : "l"(slot) : "memory");
+    if (got == e) return true;
+    uint32_t* ctl = peer_ctl(pa);
     const long long t0 = clock64();
     for (;;) {
-        if ((int32_t)(ld_relaxed_sys(p) - want) >= 0) return true;
-        if (ld_relaxed_sys(ctl_local + CTL_ERR) != 0u) return false;  // someone already gave up
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(got) : "l"(slot) : "memory");
+        if (got == e) return true;
+        if (ld_relaxed_sys(ctl + CTL_ERR) != 0u) return false;  // someone already gave up
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            st_relaxed_sys(ctl_local + CTL_ERR, code);
-            device_error(code, blockIdx.x, want);
+            st_relaxed_sys(ctl + CTL_ERR, 0x7E30u);
+            device_error(0x7E30u, blockIdx.x, e);
             return false;
         }
         __nanosleep(32);
     }
 }
-// The launch number this kernel runs as.  Stable for the kernel's whole life: only the last CTA
-// advances it, after every CTA has finished.  Call after the dependency wait.
-__device__ __forceinline__ uint32_t peer_epoch(const PeerArgs& pa) {
-    return ld_relaxed_sys(peer_ctl(pa, pa.rank) + CTL_EPOCH) + 1u;
+// Every CTA, all threads, after the CTA's own rows are written (a CTA-wide barrier precedes the
+// call): copy the peers' rows of y[M][n_total] out of the local inbox.  The grid's threads share
+// the M * n_total elements; rows [row0, row0 + n_local) are this rank's own and are skipped.
+template <bool OUT_BF16>
+__device__ __forceinline__ void peer_collect(const PeerArgs& pa, uint32_t e, size_t y_off, uint32_t M,
+                                             uint32_t n_total, uint32_t row0, uint32_t n_local) {
+    const size_t total = (size_t)M * n_total, base = y_off / (OUT_BF16 ? 2u : 4u);
+    uint8_t* y = pa.local + PEER_CTL_BYTES + y_off;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i % n_total);
+        if (row - row0 < n_local) continue;
+        uint32_t bits;
+        if (!peer_recv(pa, peer_slot(pa, pa.local, e, base + i), e, bits)) return;
+        if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[i] = (uint16_t)bits;
+        else reinterpret_cast<uint32_t*>(y)[i] = bits;
+    }
 }
-// (1) one thread of the grid, after the dependency wait.  No fence: what the signal vouches
-// for -- the completion of this rank's earlier kernels -- is given by the kernel boundary.
-__device__ __forceinline__ void peer_announce_ready(const PeerArgs& pa, uint32_t e) {
-    for (uint32_t p = 0; p < pa.world; ++p)
-        if (p != pa.rank) st_relaxed_sys(peer_ctl(pa, p) + CTL_READY + pa.rank, e);
-}
-// (2) any thread about to store into peers' arenas (the stores depend on the loads' outcome)
-__device__ __forceinline__ void peer_wait_ready(const PeerArgs& pa, uint32_t e) {
-    uint32_t* ctl = peer_ctl(pa, pa.rank);
-    for (uint32_t p = 0; p < pa.world; ++p)
-        if (p != pa.rank && !peer_wait_ge(ctl, ctl + CTL_READY + p, e, 0x7E10u + p)) return;
-}
-// (3) one thread per CTA, after all of the CTA's stores (a CTA-wide barrier precedes the call)
+// One thread per CTA, after the CTA has collected (a CTA-wide barrier precedes the call): the last
+// CTA of the grid advances the launch number.  Local atomics only.
 __device__ __forceinline__ void peer_finish(const PeerArgs& pa, uint32_t e) {
-    uint32_t* ctl = peer_ctl(pa, pa.rank);
-    __threadfence_system();  // this CTA's peer stores are performed everywhere before it is counted
-    if (atomicAdd(ctl + CTL_COUNT, 1u) != gridDim.x - 1u) return;
-    // last CTA: every CTA's stores were performed before its increment, which this thread has
-    // observed; order that observation before the signals
+    uint32_t* ctl = peer_ctl(pa);
     __threadfence();
+    if (atomicAdd(ctl + CTL_COUNT, 1u) != gridDim.x - 1u) return;
     ctl[CTL_COUNT] = 0u;
-    for (uint32_t p = 0; p < pa.world; ++p)
-        if (p != pa.rank) st_relaxed_sys(peer_ctl(pa, p) + CTL_DONE + pa.rank, e);
-    // the peers' rows were performed in this GPU's memory before their signals left; kernels
-    // that follow this one on the stream read them after the kernel boundary
-    for (uint32_t p = 0; p < pa.world; ++p)
-        if (p != pa.rank && !peer_wait_ge(ctl, ctl + CTL_DONE + p, e, 0x7E20u + p)) break;
     st_relaxed_sys(ctl + CTL_EPOCH, e);
 }
 #endif
