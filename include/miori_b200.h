@@ -210,7 +210,8 @@ int miori_linear4(const void* q, const void* s, const void* b, const void* cache
 
 /* One per rank (one process per GPU).  Each rank allocates an arena of device memory that every
  * other rank maps through CUDA IPC; outputs live at the same offset in every arena.  create
- * allocates and zeroes the arena on the current device; handle exports the 64-byte token
+ * allocates and zeroes the arena on the current device (nine times arena_bytes: the user area
+ * plus two inboxes in which the peers' rows arrive as 8-byte packets); handle exports the 64-byte token
  * (miori_peers_handle_bytes) the host passes to the other ranks by any channel; connect takes the
  * tokens of all ranks in rank order (`world` x 64 bytes, this rank's own entry ignored). */
 typedef struct miori_peers miori_peers;
@@ -227,8 +228,9 @@ int miori_peers_status(miori_peers* g);
 int miori_peers_destroy(miori_peers* g);
 
 /* miori_gemv4 / miori_gemv8 on this rank's n_local rows of an n_total-row weight matrix (q, s, b
- * point at the shard), writing y[m][row0 + n] at y_offset of EVERY rank's arena with peer stores
- * from the epilogue.  When the kernel completes on a rank, all ranks' rows have arrived there.
+ * point at the shard), delivering y[m][row0 + n] to y_offset of EVERY rank's arena: the epilogue
+ * stores the rows locally and sends them to the peers over NVLink, and collects the peers' rows
+ * before the kernel ends.  When the kernel completes on a rank, all ranks' rows are there.
  * Every rank must enqueue the same sequence of *_allgather / miori_allgather calls on its
  * group; x may be any device pointer, also one inside the arena.  y is fp32 [M][n_total] (bf16
  * with MIORI_OUT_BF16).  Requires (K / group) % 8 == 0; other shapes get MIORI_E_INVALID. */
