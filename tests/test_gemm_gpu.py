@@ -201,3 +201,22 @@ def test_strided_gemm_equals_cache_gemm_and_rejects_bad_pitch():
         check = miori_b200.check
         check(miori_b200.lib.miori_gemm_bf16_strided(A.data_ptr(), K - 8, cache.data_ptr(), K,
                                                      got.data_ptr(), N, 48, N, K, 0, None))
+
+
+def test_full_size_packed_prefill_rows_are_independent():
+    """M = 131072 token rows (64 prompts x 2048 tokens) against a 2048 x 2048 projection: every
+    1024-row block of the big product must equal the M = 1024 product of the same rows bit for
+    bit (rows are independent), checked on blocks spread over the whole range, ragged tail
+    included; the values themselves are pinned by the M = 1024 tests against the oracle."""
+    N, K, M = 2048, 2048, 131072 + 40
+    _, _, _, cache = _weights(N, K, 64, seed=55)
+    g = torch.Generator(device=DEV).manual_seed(5)
+    A = torch.randn((M, K), generator=g, device=DEV).to(torch.bfloat16)
+    big = miori_b200.gemm_bf16_cache(A, cache, N, flags=miori_b200.OUT_BF16)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(big.float()).all())
+    for r0 in (0, 1024 * 37, 1024 * 64 + 128, 131072 - 1024, 131072 - 984):
+        rows = slice(r0, min(r0 + 1024, M))
+        small = miori_b200.gemm_bf16_cache(A[rows].contiguous(), cache, N, flags=miori_b200.OUT_BF16)
+        assert torch.equal(small, big[rows]), f"rows {r0}.. differ"
+    assert miori_b200.lib.miori_device_error_poll() == 0
