@@ -480,6 +480,10 @@ def main():
 
     if rank == 0 and not args.no_extras and world == 1:
         out["extras"] = extras(torch, miori_b200, synth, dev, G, peaks, timed)
+    if not args.no_extras and grp is not None:
+        c1 = config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world, grp)
+        if rank == 0:
+            out.setdefault("extras", {})["config1_gemv8_sharded"] = c1
     if not args.no_extras:
         # every rank takes part: the large prefill GEMM is sharded by token rows, no collective
         c4 = config4_prefill(torch, miori_b200, synth, dev, G, peaks, timed, rank, world)
@@ -503,6 +507,41 @@ def main():
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world, grp):
+    """BASELINE config 1 on N > 1 GPUs: the 8-bit head (N=131072, K=2048, M=1, bf16 logits) with
+    its rows split over the ranks and the logits gathered by the GEMV's own epilogue.  Every rank
+    cycles through a pool of distinct shards larger than L2; GB/s counts the whole matrix."""
+    N, K = 131072, 2048
+    rows = N // world
+    shard_bytes = packed_bytes(rows, K, 8, G)
+    npool = max(2, -(-(300 << 20) // shard_bytes))
+    pool = []
+    for i in range(npool):  # same seeds on every rank: shard `rank` of matrix i
+        g = torch.Generator(device=dev).manual_seed(4000 + i * 64 + rank)
+        q = torch.randint(-2**31, 2**31 - 1, (rows, K // 4), generator=g, device=dev, dtype=torch.int64).to(torch.int32)
+        sc = (torch.rand((rows, K // G), generator=g, device=dev) * 1e-3 + 1e-4).to(torch.bfloat16)
+        bi = (torch.rand((rows, K // G), generator=g, device=dev) * -0.1).to(torch.bfloat16)
+        pool.append((q, sc, bi))
+    x = synth.make_activation(1, K, seed=9, device=dev)
+    off = grp.alloc(N * 2)
+    flags = miori_b200.LAUNCH_PDL | miori_b200.OUT_BF16
+
+    def run():
+        for q, sc, bi in pool:
+            grp.gemv_allgather(8, q, sc, bi, x, off, rank * rows, N, group=G, flags=flags)
+    run()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    ms = timed(g.replay, 10) / 10 / npool
+    by = packed_bytes(N, K, 8, G)
+    return {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
+            "n_gpus": world, "rows_per_gpu": rows, "pool": npool, "out": "bf16",
+            "how": "CUDA graph of dependent launches over a pool of distinct shards (> L2 per "
+                   "rank); every launch ends with the whole logits vector on every rank"}
 
 
 def config4_prefill(torch, miori_b200, synth, dev, G, peaks, timed, rank, world):
