@@ -69,3 +69,24 @@ def test_ops_refuse_cpu_tensors():
     x = torch.zeros((1, 64), dtype=torch.bfloat16)
     with pytest.raises(ValueError, match="no CPU path"):
         miori_b200.gemv4(q, s, s, x)
+
+
+def test_strided_gemm_and_peer_entries_reject_bad_arguments():
+    ok = 0x1000
+    # a row pitch shorter than the row, empty shapes, null pointers
+    assert lib.miori_gemm_bf16_strided(ok, 56, ok, 64, ok, 64, 8, 64, 64, 0, None) == -1
+    assert b"pitch" in lib.miori_last_error()
+    assert lib.miori_gemm_bf16_strided(ok, 64, ok, 64, ok, 32, 8, 64, 64, 0, None) == -1
+    assert lib.miori_gemm_bf16_strided(ok, 64, None, 64, ok, 64, 8, 64, 64, 0, None) == -1
+    assert lib.miori_gemm_bf16_strided(ok, 64, ok, 64, ok, 64, 0, 64, 64, 0, None) == -1
+    # peer groups: rank outside the world, too many ranks, arena size not a multiple of 256
+    h = C.c_void_p()
+    assert lib.miori_peers_create(2, 2, 1 << 20, C.byref(h)) == -1 and h.value is None
+    assert lib.miori_peers_create(0, 9, 1 << 20, C.byref(h)) == -1
+    assert lib.miori_peers_create(0, 1, 1000, C.byref(h)) == -1
+    assert b"256" in lib.miori_last_error()
+    assert lib.miori_peers_handle_bytes() == 64
+    assert lib.miori_gemv4_allgather(None, ok, ok, ok, ok, 0, 16, 0, 16, 64, 1, 64, 0, None) == -1
+    assert lib.miori_allgather(None, ok, 0, 1, 16, 0, 16, 4, 0, None) == -1
+    assert lib.miori_peers_status(None) == -1
+    assert lib.miori_peers_destroy(None) == 0
