@@ -456,9 +456,9 @@ def main():
     peaks, peak_kind = measured_peaks()
     m1 = per_m["1"]
     # DRAM bytes (read + write) per algorithmic byte of gemv_tma_kernel, from the ncu capture
-    # summarised in profiles/gemv_tma_n131072_k2048_m1.md (156.8 MB moved for 151.0 MB of
+    # summarised in profiles/gemv_tma_n131072_k2048_m1.md (156.1 MB moved for 151.0 MB of
     # weights); traffic grows in proportion to the weights a launch streams
-    DRAM_PER_ALGO_BYTE = 1.038
+    DRAM_PER_ALGO_BYTE = 1.034
     roofline = {
         "kernel": "gemv_tma_kernel<4,exact,1> (M=1 pass of the stack, 96 launches per pass)",
         "bound": "hbm", "achieved": m1["gbs"] / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",

@@ -98,3 +98,36 @@ extern "C" __attribute__((visibility("default"))) int miori_shim_test_prefill(
         return -1;
     }
 }
+
+// The reference's test-gemm-naive procedure (src/main.cpp:561-610): C = A x B^T on bf16 operands
+// with row pitches and byte offsets into larger buffers, result read back through contents().
+extern "C" __attribute__((visibility("default"))) int miori_shim_test_naive(
+    const uint16_t* A, const uint16_t* B, float* C, uint32_t M, uint32_t N, uint32_t K, uint32_t lda,
+    uint32_t ldb, uint32_t ldc) {
+    using namespace miori;
+    try {
+        Metal m;
+        std::string err;
+        if (!m.init("", err)) throw std::runtime_error(err);
+        const uint32_t aoff = 512, boff = 1024, coff = 256;  // byte offsets, as the engines pass them
+        MTL::Buffer* bA = m.new_buffer(aoff + (size_t)M * lda * 2);
+        MTL::Buffer* bB = m.new_buffer(boff + (size_t)N * ldb * 2);
+        MTL::Buffer* bC = m.new_buffer(coff + (size_t)M * ldc * 4);
+        std::memcpy((char*)bA->contents() + aoff, A, (size_t)M * lda * 2);
+        std::memcpy((char*)bB->contents() + boff, B, (size_t)N * ldb * 2);
+        std::memset(bC->contents(), 0, coff + (size_t)M * ldc * 4);
+        auto* cb = m.begin();
+        auto* e = cb->computeCommandEncoder();
+        gemm_naive(m, e, bA, bB, bC, M, N, K, lda, ldb, ldc, aoff, boff, coff);
+        e->endEncoding();
+        m.submit(cb, true);
+        std::memcpy(C, (char*)bC->contents() + coff, (size_t)M * ldc * 4);
+        bA->release();
+        bB->release();
+        bC->release();
+        return 0;
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return -1;
+    }
+}

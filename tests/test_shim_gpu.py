@@ -23,6 +23,7 @@ def shim():
     p, u = C.c_void_p, C.c_uint32
     lib.miori_shim_test_gemv.argtypes = [C.c_int, p, p, p, p, p, u, u, u]
     lib.miori_shim_test_prefill.argtypes = [p, p, p, p, p, p, u, u, u]
+    lib.miori_shim_test_naive.argtypes = [p, p, p, u, u, u, u, u, u]
     return lib
 
 
@@ -59,6 +60,24 @@ def test_prefill_through_operator_api(shim, port):
     assert np.array_equal(c32, c64)
     want = port.gemm_bf16(An, port.dequant_rowmajor(4, qn, sn, bn, 32))
     assert_close(c64, want, rel_max=1e-4, what="shim prefill")
+
+
+@pytest.mark.parametrize("M,N,K,lda,ldb,ldc", [(40, 16, 2048, 2048, 2048, 16), (130, 128, 200, 208, 4096, 2048),
+                                               (37, 50, 70, 77, 71, 53)])
+def test_gemm_naive_through_operator_api(shim, port, M, N, K, lda, ldb, ldc):
+    """gemm_naive with row pitches and byte offsets (the gate projection, the probabilities x V
+    product, and a shape with odd pitches that takes the plain kernel)."""
+    import torch
+    g = torch.Generator().manual_seed(M + N)
+    A = torch.randn((M, lda), generator=g).to(torch.bfloat16)
+    B = torch.randn((N, ldb), generator=g).to(torch.bfloat16)
+    An, Bn = u16(A), u16(B)
+    Cn = np.zeros((M, ldc), np.float32)
+    rc = shim.miori_shim_test_naive(An.ctypes.data, Bn.ctypes.data, Cn.ctypes.data, M, N, K, lda, ldb, ldc)
+    assert rc == 0, shim.miori_shim_last_error()
+    want = port.gemm_bf16(np.ascontiguousarray(An[:, :K]), np.ascontiguousarray(Bn[:, :K]))
+    assert_close(Cn[:, :N], want, rel_max=1e-4, what="shim gemm_naive")
+    assert not Cn[:, N:].any()
 
 
 def test_errors_surface_as_messages(shim):
