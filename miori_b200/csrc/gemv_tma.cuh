@@ -67,6 +67,24 @@ __device__ __forceinline__ float ldsf32(uint32_t a) {
     return v;
 }
 
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+// two floats -> packed fp16 pair (lo, hi), round to nearest even
+__device__ __forceinline__ uint32_t f16x2_bits(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// a float rounded to fp16 and back: the value the tensor core will see
+__device__ __forceinline__ float through_f16(float v) {
+    float r;
+    asm("{\n\t.reg .b16 h;\n\tcvt.rn.f16.f32 h, %1;\n\tcvt.f32.f16 %0, h;\n\t}" : "=f"(r) : "f"(v));
+    return r;
+}
+
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -75,13 +93,14 @@ __device__ __forceinline__ uint32_t x_unit(uint32_t step, uint32_t t, uint32_t w
     return step * STEP_UNITS + 4u * t + 2u * (t >> 1) + wd;
 }
 
-// Stage x for the MMA B operand: permuted to the k order of the A fragments (plus 16*x for
-// 8-bit codes), laid out by x_unit(); for EXACT also the fp32 sum of x over every chunk (PAIR:
-// over every pair of chunks, i.e. every 64-weight group).
+// Stage x for the MMA B operand: permuted to the k order of the A fragments (8-bit codes: as
+// fp16 scaled by `mul`), laid out by x_unit(); for EXACT also the fp32 sum of x over every chunk
+// (PAIR: over every pair of chunks, i.e. every 64-weight group).
 template <int BITS, bool EXACT, int MP, bool PAIR>
 __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, uint4* xs,
                                                float* xsum, uint32_t M, uint32_t K,
-                                               uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
+                                               uint32_t steps_p, uint32_t pitch, uint32_t cpr,
+                                               float mul) {
     constexpr int CW = 128 / BITS, KU = BITS == 4 ? 8 : 4;
     const uint32_t upr = steps_p * 16u;  // logical units per row
     for (uint32_t i = threadIdx.x; i < (uint32_t)MP * upr; i += THREADS) {
@@ -95,14 +114,12 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
                 o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
                 o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3,x7)
             } else {
+                // 8-bit codes go to the tensor core as fp16 (1024 + code), so x goes as fp16 too,
+                // scaled by a power of two that keeps the row's largest value below 2^15; the
+                // unit holds (x0,x2) and (x1,x3), the k order of the byte pairs the unpack makes
                 const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + (size_t)m * K) + u);
-                const uint32_t x02 = __byte_perm(v.x, v.y, 0x5410);  // (x0,x2)
-                const uint32_t x13 = __byte_perm(v.x, v.y, 0x7632);  // (x1,x3)
-                const uint32_t sixteen = 0x41804180u, zero = 0u;     // bf16 16.0 pair
-                o.x = x02;
-                o.y = gemvmma::bf16x2_fma(x02, sixteen, zero);
-                o.z = x13;
-                o.w = gemvmma::bf16x2_fma(x13, sixteen, zero);
+                o.x = f16x2_bits(bf16lo(v.x) * mul, bf16lo(v.y) * mul);
+                o.y = f16x2_bits(bf16hi(v.x) * mul, bf16hi(v.y) * mul);
             }
         }
         xs[(size_t)m * pitch + x_unit(u >> 4, (u >> 2) & 3u, u & 3u)] = o;
@@ -119,8 +136,15 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
 #pragma unroll
                 for (int j = 0; j < (PAIR ? 2 : 1) * CW / 8; ++j) {
                     const uint4 v = __ldg(xp + j);
-                    sum += bf16lo(v.x); sum += bf16hi(v.x); sum += bf16lo(v.y); sum += bf16hi(v.y);
-                    sum += bf16lo(v.z); sum += bf16hi(v.z); sum += bf16lo(v.w); sum += bf16hi(v.w);
+                    if (BITS == 4) {
+                        sum += bf16lo(v.x); sum += bf16hi(v.x); sum += bf16lo(v.y); sum += bf16hi(v.y);
+                        sum += bf16lo(v.z); sum += bf16hi(v.z); sum += bf16lo(v.w); sum += bf16hi(v.w);
+                    } else {  // the sum of exactly the fp16 values staged above
+                        sum += through_f16(bf16lo(v.x) * mul); sum += through_f16(bf16hi(v.x) * mul);
+                        sum += through_f16(bf16lo(v.y) * mul); sum += through_f16(bf16hi(v.y) * mul);
+                        sum += through_f16(bf16lo(v.z) * mul); sum += through_f16(bf16hi(v.z) * mul);
+                        sum += through_f16(bf16lo(v.w) * mul); sum += through_f16(bf16hi(v.w) * mul);
+                    }
                 }
             }
             xsum[i] = sum;
@@ -202,7 +226,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     constexpr int KC = 16 * SK;             // k per slab: 16 steps, 4 per warp of a group
     static_assert(!PAIR || (EXACT && NT == 1 && BITS == 4), "PAIR is an EXACT 4-bit single-set mode");
     constexpr int MP = EXACT ? (PAIR ? 4 : 2 * NT) : 8 * NT;
-    constexpr float OFF = BITS == 4 ? 128.0f : 2176.0f;  // sum of the 128 offsets per code
+    constexpr float OFF = BITS == 4 ? 128.0f : 1024.0f;  // what the unpack adds to every code
     constexpr uint32_t MASK = 0x000F000Fu, MAGIC = 0x43004300u;  // bf16 128.0 in both halves
 
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -227,6 +251,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __shared__ __align__(8) uint64_t full_bars[MAX_STAGES];
     __shared__ __align__(8) uint64_t empty_bars[MAX_STAGES];
     __shared__ volatile uint32_t abort_flag;
+    __shared__ volatile uint32_t x_maxbits;  // 8-bit codes: largest |x| bit pattern of the staged rows
+    __shared__ float x_rescale;              // 8-bit codes: undoes the fp16 staging scale at the store
     uint8_t* ring = smem_raw;                                            // [nstage][STAGE_BYTES]
     uint4* xs = reinterpret_cast<uint4*>(ring + (size_t)nstage * STAGE_BYTES);  // [MP][pitch]
     uint4* zeros = xs + (size_t)MP * pitch;                              // ZERO_BYTES of zeros
@@ -295,6 +321,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const bool producer = threadIdx.x == WARPS * 32;
     if (producer) {
         abort_flag = 0u;
+        x_maxbits = 0u;
         for (uint32_t i = 0; i < nstage; ++i) {
             mbar_init(smem_addr(&full_bars[i]), 1);
             mbar_init(smem_addr(&empty_bars[i]), 4);
@@ -315,6 +342,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t world = SHARDED ? pa.world : 0u;
     // one output element: y[m][row0 + row]
     auto store_out = [&](uint32_t m, uint32_t row, float v) {
+        if (BITS == 8) v *= x_rescale;
         const size_t idx = (size_t)m * n_total + row0 + row;
         const uint32_t bits = OUT_BF16 ? float_to_bf16_bits(v) : __float_as_uint(v);
         if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)bits;
@@ -331,10 +359,33 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     // one-pass staging where it measured faster: one slab of K, and either the roomy
     // instantiation or at most two staged rows
-    if ((ROOMY || MP <= 2) && kslabs == 1u)
+    float xmul = 1.0f;
+    if constexpr (BITS == 8) {
+        // power-of-two scale for the fp16 staging: the largest |x| of the staged rows lands in
+        // [2^14, 2^15); the outputs are multiplied back at the store
+        __syncthreads();  // x_maxbits was cleared before the wait
+        uint32_t mx = 0;
+        const uint4* x4 = reinterpret_cast<const uint4*>(x);
+        for (uint32_t i = threadIdx.x; i < M * (K / 8u); i += THREADS) {
+            const uint4 v = __ldg(x4 + i);
+            const uint32_t a = v.x & 0x7FFF7FFFu, b = v.y & 0x7FFF7FFFu, c = v.z & 0x7FFF7FFFu,
+                           d = v.w & 0x7FFF7FFFu;
+            mx = max(max(max(mx, a & 0xFFFFu), max(a >> 16, b & 0xFFFFu)),
+                     max(max(b >> 16, c & 0xFFFFu), max(max(c >> 16, d & 0xFFFFu), d >> 16)));
+        }
+        mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+        if (lane == 0 && mx) atomicMax(const_cast<uint32_t*>(&x_maxbits), mx);
+        __syncthreads();
+        const uint32_t top = x_maxbits;
+        int sh = top ? (int)((top >> 7) & 0xFFu) - 141 : 0;  // bf16 exponent field - 127 - 14
+        sh = max(-100, min(110, sh));
+        xmul = __uint_as_float((uint32_t)(127 - sh) << 23);
+        if (threadIdx.x == 0) x_rescale = __uint_as_float((uint32_t)(127 + sh) << 23);
+    }
+    if (BITS == 4 && (ROOMY || MP <= 2) && kslabs == 1u)
         stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     else
-        stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+        stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, xmul);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
@@ -427,6 +478,26 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         s2a = s0 | (s0 << 16); b2a = b0 | (b0 << 16);
                         s2b = s1 | (s1 << 16); b2b = b1 | (b1 << 16);
                     }
+                    if constexpr (BITS == 8) {
+                        // bytes (b0,b2) and (b1,b3) of a word become two fp16 pairs 1024 + code:
+                        // two masks and one shift per word, one MMA per word
+                        constexpr uint32_t BMASK = 0x00FF00FFu, HMAGIC = 0x64006400u;
+#pragma unroll
+                        for (int wd = 0; wd < 4; ++wd) {
+                            const uint32_t a0 = lop3_and_or(w0[wd], BMASK, HMAGIC);
+                            const uint32_t a1 = lop3_and_or(w0[wd] >> 8, BMASK, HMAGIC);
+                            const uint32_t c0 = lop3_and_or(w1[wd], BMASK, HMAGIC);
+                            const uint32_t c1 = lop3_and_or(w1[wd] >> 8, BMASK, HMAGIC);
+#pragma unroll
+                            for (int j = 0; j < NT; ++j) {
+                                const uint2 xu = lds64(xa[j] + wd * 16);
+                                if (wd == 0) mma_f16_z(d0[j], a0, c0, a1, c1, xu.x, xu.y);
+                                else if (wd == 1) mma_f16_z(d1[j], a0, c0, a1, c1, xu.x, xu.y);
+                                else if (wd == 2) mma_f16(d0[j], a0, c0, a1, c1, xu.x, xu.y);
+                                else mma_f16(d1[j], a0, c0, a1, c1, xu.x, xu.y);
+                            }
+                        }
+                    } else {
 #pragma unroll
                     for (int wd = 0; wd < 4; ++wd) {
                         uint32_t a[4], c[4];  // pairs (n0,n4),(n1,n5),(n2,n6),(n3,n7), rows g, g+8
@@ -449,6 +520,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                             if (wd & 1) mma_bf16(d1[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
                             else mma_bf16(d0[j], a[2], c[2], a[3], c[3], xu.z, xu.w);
                         }
+                    }
                     }
                     if (EXACT) {
                         const float sc0 = __uint_as_float(s0 << 16);
