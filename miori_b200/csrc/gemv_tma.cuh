@@ -100,7 +100,7 @@ template <int BITS, bool EXACT, int MP, bool PAIR>
 __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, uint4* xs,
                                                float* xsum, uint32_t M, uint32_t K,
                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr,
-                                               float mul) {
+                                               const float* mul_rows) {
     constexpr int CW = 128 / BITS, KU = BITS == 4 ? 8 : 4;
     const uint32_t upr = steps_p * 16u;  // logical units per row
     for (uint32_t i = threadIdx.x; i < (uint32_t)MP * upr; i += THREADS) {
@@ -115,9 +115,10 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
                 o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3,x7)
             } else {
                 // 8-bit codes go to the tensor core as fp16 (1024 + code), so x goes as fp16 too,
-                // scaled by a power of two that keeps the row's largest value below 2^15; the
+                // scaled by the row's power of two that keeps its largest value below 2^15; the
                 // unit holds (x0,x2) and (x1,x3), the k order of the byte pairs the unpack makes
                 const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + (size_t)m * K) + u);
+                const float mul = mul_rows[m];
                 o.x = f16x2_bits(bf16lo(v.x) * mul, bf16lo(v.y) * mul);
                 o.y = f16x2_bits(bf16hi(v.x) * mul, bf16hi(v.y) * mul);
             }
@@ -130,6 +131,7 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
             const uint32_t m = i / cpr, c = i - m * cpr;
             float sum = 0.0f;
             if (m < M && c < chunks) {
+                const float mul = BITS == 8 ? mul_rows[m] : 1.0f;
                 // PAIR: both chunks of a 64-weight group carry the sum over the whole group
                 const uint32_t c0 = PAIR ? (c & ~1u) : c;
                 const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c0 * CW);
@@ -251,8 +253,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __shared__ __align__(8) uint64_t full_bars[MAX_STAGES];
     __shared__ __align__(8) uint64_t empty_bars[MAX_STAGES];
     __shared__ volatile uint32_t abort_flag;
-    __shared__ volatile uint32_t x_maxbits;  // 8-bit codes: largest |x| bit pattern of the staged rows
-    __shared__ float x_rescale;              // 8-bit codes: undoes the fp16 staging scale at the store
+    __shared__ uint32_t x_maxbits[4];  // 8-bit codes: largest |x| bit pattern of each staged row
+    __shared__ float x_mul[4];         // 8-bit codes: per-row power-of-two scale of the fp16 staging
+    __shared__ float x_rescale[4];     // ... and its inverse, applied at the store
     uint8_t* ring = smem_raw;                                            // [nstage][STAGE_BYTES]
     uint4* xs = reinterpret_cast<uint4*>(ring + (size_t)nstage * STAGE_BYTES);  // [MP][pitch]
     uint4* zeros = xs + (size_t)MP * pitch;                              // ZERO_BYTES of zeros
@@ -321,7 +324,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const bool producer = threadIdx.x == WARPS * 32;
     if (producer) {
         abort_flag = 0u;
-        x_maxbits = 0u;
+        x_maxbits[0] = x_maxbits[1] = x_maxbits[2] = x_maxbits[3] = 0u;
         for (uint32_t i = 0; i < nstage; ++i) {
             mbar_init(smem_addr(&full_bars[i]), 1);
             mbar_init(smem_addr(&empty_bars[i]), 4);
@@ -342,7 +345,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t world = SHARDED ? pa.world : 0u;
     // one output element: y[m][row0 + row]
     auto store_out = [&](uint32_t m, uint32_t row, float v) {
-        if (BITS == 8) v *= x_rescale;
+        if (BITS == 8) v *= x_rescale[m];
         const size_t idx = (size_t)m * n_total + row0 + row;
         const uint32_t bits = OUT_BF16 ? float_to_bf16_bits(v) : __float_as_uint(v);
         if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)bits;
@@ -359,33 +362,40 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     // one-pass staging where it measured faster: one slab of K, and either the roomy
     // instantiation or at most two staged rows
-    float xmul = 1.0f;
     if constexpr (BITS == 8) {
-        // power-of-two scale for the fp16 staging: the largest |x| of the staged rows lands in
-        // [2^14, 2^15); the outputs are multiplied back at the store
+        // per-row power-of-two scale for the fp16 staging: the row's largest |x| lands in
+        // [2^14, 2^15); the outputs are multiplied back at the store.  Per row, so that a row's
+        // result does not depend on its neighbours in the batch.
+        static_assert(MP <= 4, "8-bit rows staged per launch");
         __syncthreads();  // x_maxbits was cleared before the wait
-        uint32_t mx = 0;
+        const uint32_t upr8 = K / 8u;  // 16-byte pieces per row
         const uint4* x4 = reinterpret_cast<const uint4*>(x);
-        for (uint32_t i = threadIdx.x; i < M * (K / 8u); i += THREADS) {
-            const uint4 v = __ldg(x4 + i);
-            const uint32_t a = v.x & 0x7FFF7FFFu, b = v.y & 0x7FFF7FFFu, c = v.z & 0x7FFF7FFFu,
-                           d = v.w & 0x7FFF7FFFu;
-            mx = max(max(max(mx, a & 0xFFFFu), max(a >> 16, b & 0xFFFFu)),
-                     max(max(b >> 16, c & 0xFFFFu), max(max(c >> 16, d & 0xFFFFu), d >> 16)));
+        for (uint32_t m = 0; m < M; ++m) {
+            uint32_t mx = 0;
+            for (uint32_t i = threadIdx.x; i < upr8; i += THREADS) {
+                const uint4 v = __ldg(x4 + (size_t)m * upr8 + i);
+                const uint32_t a = v.x & 0x7FFF7FFFu, b = v.y & 0x7FFF7FFFu, c = v.z & 0x7FFF7FFFu,
+                               d = v.w & 0x7FFF7FFFu;
+                mx = max(max(max(mx, a & 0xFFFFu), max(a >> 16, b & 0xFFFFu)),
+                         max(max(b >> 16, c & 0xFFFFu), max(max(c >> 16, d & 0xFFFFu), d >> 16)));
+            }
+            mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+            if (lane == 0 && mx) atomicMax(&x_maxbits[m], mx);
         }
-        mx = __reduce_max_sync(0xFFFFFFFFu, mx);
-        if (lane == 0 && mx) atomicMax(const_cast<uint32_t*>(&x_maxbits), mx);
         __syncthreads();
-        const uint32_t top = x_maxbits;
-        int sh = top ? (int)((top >> 7) & 0xFFu) - 141 : 0;  // bf16 exponent field - 127 - 14
-        sh = max(-100, min(110, sh));
-        xmul = __uint_as_float((uint32_t)(127 - sh) << 23);
-        if (threadIdx.x == 0) x_rescale = __uint_as_float((uint32_t)(127 + sh) << 23);
+        if (threadIdx.x < 4u) {
+            const uint32_t top = x_maxbits[threadIdx.x];
+            int sh = top ? (int)((top >> 7) & 0xFFu) - 141 : 0;  // bf16 exponent field - 127 - 14
+            sh = max(-100, min(110, sh));
+            x_mul[threadIdx.x] = __uint_as_float((uint32_t)(127 - sh) << 23);
+            x_rescale[threadIdx.x] = __uint_as_float((uint32_t)(127 + sh) << 23);
+        }
+        __syncthreads();
     }
     if (BITS == 4 && (ROOMY || MP <= 2) && kslabs == 1u)
         stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
     else
-        stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, xmul);
+        stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, x_mul);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();

@@ -222,3 +222,26 @@ def test_runtime_buffers_and_copies(port):
         for h in bufs:
             lib.miori_buffer_free(h)
         lib.miori_device_close(dev)
+
+
+def test_gemv8_activation_range(port):
+    """8-bit codes meet x as fp16 scaled by a power of two taken from the largest |x|: scaling x
+    by a power of two must scale y exactly, an outlier must not cost the other terms their
+    precision, rows keep their own scale, and zeros must stay zeros."""
+    N, K = 1024, 2048
+    q, s, b, x = _case(8, N, K, 2, 64, seed=808)
+    y = _run(8, q, s, b, x, 64)
+    for k in (20, -30, 100):
+        xs = (x.float() * 2.0 ** k).to(torch.bfloat16)
+        ys = _run(8, q, s, b, xs, 64)
+        assert np.array_equal(ys, y * np.float32(2.0 ** k)), f"x * 2^{k}"
+    xo = x.clone()
+    xo[0, 7] = 3.0e4   # one huge activation in row 0
+    xo[1, :] = (xo[1, :].float() * 2.0 ** -40).to(torch.bfloat16)  # a very quiet row beside it
+    want = port.gemv(8, u32(q), u16(s), u16(b), u16(xo), 64)
+    got = _run(8, q, s, b, xo, 64)
+    assert_close(got[0], want[0], rel_max=TOL_EXACT_PATH, what="row with an outlier")
+    assert_close(got[1], want[1], rel_max=TOL_EXACT_PATH, what="quiet row next to the outlier")
+    alone = _run(8, q, s, b, xo[1:2].contiguous(), 64)
+    assert np.array_equal(alone[0], got[1]), "a row's value depends on its neighbour"
+    assert not _run(8, q, s, b, torch.zeros_like(x), 64).any()
