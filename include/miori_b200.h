@@ -44,16 +44,6 @@ extern "C" {
                                   must be immutable while in flight) and waits for the
                                   predecessor before touching x / A or writing y / C */
 #define MIORI_GEMV_EXACT 4u    /* force the fp32-dequant GEMV path for every M (default: M<=4) */
-/* Kernel-selection overrides, for tests and A/B timing only.  Every choice computes the same
- * result; the default heuristics pick among them by shape. */
-#define MIORI_TUNE_GEMM_NARROW 0x100u  /* GEMM: 128x128 tiles */
-#define MIORI_TUNE_GEMM_WIDE 0x200u    /* GEMM: 128x256 tiles, one CTA per tile */
-#define MIORI_TUNE_GEMV_SIMT 0x400u    /* GEMV: the scalar-FMA kernel */
-#define MIORI_TUNE_GEMV_LDG 0x800u     /* GEMV: tensor-core kernel fed by plain loads (no TMA) */
-#define MIORI_TUNE_GEMV_TILED 0x2000u  /* GEMV: tiled TMA even where linear bulk copies fit */
-#define MIORI_TUNE_GEMM_PAIR 0x4000u   /* GEMM: two-CTA (cta_group::2) kernel */
-#define MIORI_TUNE_GEMM_NOPAIR 0x8000u /* GEMM: never the two-CTA kernel */
-
 const char* miori_last_error(void);
 /* Library version string, e.g. "miori_b200 0.1 sm_100a". */
 const char* miori_version(void);
@@ -166,7 +156,9 @@ int miori_gemm_bf16_cache_ws(const void* A, const void* cache, void* C, uint32_t
  * to a 16 MiB array built into the library (miori_gemm_static_scratch_bytes); every GPU that
  * loads the library holds that array until the process exits.  The call allocates nothing --
  * no cudaMalloc / cudaFree, no allocating library routine.  Shapes whose preferred split needs
- * more than the array are refused with MIORI_E_INVALID and a message that names the sizes;
+ * more than the array are refused with MIORI_E_INVALID and a message that names the sizes
+ * (miori_gemm_bf16_cache still runs them, unsplit and without scratch; compare
+ * miori_gemm_workspace_bytes with miori_gemm_static_scratch_bytes to know beforehand);
  * shapes that do not split at all run without touching it.  The first call on a device looks
  * up the array's device address, so make that call before starting any stream capture.  All
  * calls share the one array: it keeps whatever the last call left (nothing needs clearing,
@@ -221,9 +213,14 @@ int miori_peers_handle(miori_peers* g, void* handle_out);
 int miori_peers_connect(miori_peers* g, const void* handles);
 void* miori_peers_arena(miori_peers* g);        /* local arena (device pointer), offset 0 */
 size_t miori_peers_arena_bytes(miori_peers* g);
-/* MIORI_E_DEVICE if a kernel on this rank gave up waiting for a peer (bounded waits, about a
- * second); the group is unusable afterwards. */
+/* MIORI_E_DEVICE if a kernel on this rank gave up waiting for a peer; the group is unusable
+ * afterwards.  Every wait for a peer is bounded: about a second unless miori_peers_set_wait_us
+ * gives another limit (1 us .. 10 s; call it with no kernel of the group in flight).  The limit
+ * also bounds how far apart in time the ranks may ENQUEUE the same launch: a rank whose launch
+ * comes later than that after its peers' (first-use module load, graph instantiation, a paused
+ * host thread) makes them give up, so put a host barrier between set-up and the first launch. */
 int miori_peers_status(miori_peers* g);
+int miori_peers_set_wait_us(miori_peers* g, uint32_t microseconds);
 /* Call only when no rank has kernels in flight that store into this rank's arena. */
 int miori_peers_destroy(miori_peers* g);
 

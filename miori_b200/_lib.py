@@ -59,6 +59,7 @@ _SIGS = {
     "miori_peers_arena": (_p, [_p]),
     "miori_peers_arena_bytes": (_sz, [_p]),
     "miori_peers_status": (_i, [_p]),
+    "miori_peers_set_wait_us": (_i, [_p, _u32]),
     "miori_peers_destroy": (_i, [_p]),
     "miori_gemv4_allgather": (_i, [_p, _p, _p, _p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_gemv8_allgather": (_i, [_p, _p, _p, _p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _p]),

@@ -7,6 +7,7 @@
 #include <cstdio>
 
 #include "../../include/miori_b200.h"
+#include "tune.h"
 
 #define MIORI_API extern "C" __attribute__((visibility("default")))
 

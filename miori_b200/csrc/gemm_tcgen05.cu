@@ -916,7 +916,8 @@ MIORI_API int miori_gemm_bf16_strided(const void* A, uint32_t lda, const void* B
 constexpr size_t kStaticScratchBytes = (size_t)16 << 20;  // 16 MiB
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
 
-// Device address of g_static_scratch on the current device (looked up on first use there).
+// Device address of g_static_scratch on the current device (looked up on first use there).  As
+// for every launch entry, the device current at the call must be the one the stream belongs to.
 static int static_scratch_ptr(float** out) {
     static float* ptrs[64];
     static std::mutex mu;
@@ -946,7 +947,9 @@ MIORI_API int miori_gemm_bf16_cache_static(const void* A, const void* cache, voi
     if (need > kStaticScratchBytes)
         return fail(MIORI_E_INVALID,
                     "miori_gemm_bf16_cache_static: M=%u N=%u K=%u needs %zu bytes of scratch (%u "
-                    "K-splits), the built-in scratch holds %zu; use miori_gemm_bf16_cache_ws",
+                    "K-splits), the built-in scratch holds %zu; miori_gemm_bf16_cache runs the shape "
+                    "without a K split and without scratch (miori_gemm_bf16_cache_ws splits it given a "
+                    "caller workspace)",
                     M, N, K, need, want.splits, kStaticScratchBytes);
     float* ws = nullptr;
     if (want.splits > 1) {

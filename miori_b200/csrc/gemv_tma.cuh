@@ -164,7 +164,8 @@ template <int BITS, bool EXACT, int MP, bool PAIR>
 __device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, uint4* xs,
                                                 float* xsum, uint32_t M, uint32_t K,
                                                 uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
-    constexpr int KU = BITS == 4 ? 8 : 4;
+    static_assert(BITS == 4, "one-pass staging exists for 4-bit codes only (8-bit x is staged as scaled fp16)");
+    constexpr int KU = 8;
     const uint32_t upr = steps_p * 16u;  // logical units per row
     const uint32_t total = (uint32_t)MP * upr, lane = threadIdx.x & 31u;
     for (uint32_t i0 = threadIdx.x - lane; i0 < total; i0 += THREADS) {
@@ -173,26 +174,14 @@ __device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, 
         uint4 o = make_uint4(0u, 0u, 0u, 0u);
         float sum = 0.0f;
         if (i < total && m < M && u * KU < K) {
-            if (BITS == 4) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
-                o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0,x4)
-                o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1,x5)
-                o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
-                o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3,x7)
-                if (EXACT)
-                    sum = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
-                          ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
-            } else {
-                const uint2 v = __ldg(reinterpret_cast<const uint2*>(x + (size_t)m * K) + u);
-                const uint32_t x02 = __byte_perm(v.x, v.y, 0x5410);  // (x0,x2)
-                const uint32_t x13 = __byte_perm(v.x, v.y, 0x7632);  // (x1,x3)
-                const uint32_t sixteen = 0x41804180u, zero = 0u;     // bf16 16.0 pair
-                o.x = x02;
-                o.y = gemvmma::bf16x2_fma(x02, sixteen, zero);
-                o.z = x13;
-                o.w = gemvmma::bf16x2_fma(x13, sixteen, zero);
-                if (EXACT) sum = (bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y));
-            }
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
+            o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0,x4)
+            o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1,x5)
+            o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
+            o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3,x7)
+            if (EXACT)
+                sum = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
+                      ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
         }
         if (i < total) xs[(size_t)m * pitch + x_unit(u >> 4, (u >> 2) & 3u, u & 3u)] = o;
         if (EXACT) {
@@ -392,10 +381,14 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         __syncthreads();
     }
-    if (BITS == 4 && (ROOMY || MP <= 2) && kslabs == 1u)
-        stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
-    else
-        stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, x_mul);
+    bool staged = false;
+    if constexpr (BITS == 4) {
+        if ((ROOMY || MP <= 2) && kslabs == 1u) {
+            stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+            staged = true;
+        }
+    }
+    if (!staged) stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, x_mul);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();

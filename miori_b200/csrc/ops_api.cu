@@ -4,6 +4,7 @@
 #include "gemv_mma.cuh"
 #include "gemv_simt.cuh"
 #include "gemv_tma.cuh"
+#include "gemv_umma.cuh"
 
 using namespace miori_b200;
 
@@ -33,6 +34,13 @@ int gemv_entry(const char* op, const void* q, const void* s, const void* b, cons
     const bool force_exact = (flags & MIORI_GEMV_EXACT) != 0;
     const bool force_simt = (flags & MIORI_TUNE_GEMV_SIMT) != 0;  // tuning override: shape-agnostic SIMT path
     const bool no_bulk = (flags & MIORI_TUNE_GEMV_LDG) != 0;     // tuning override: register-streaming kernel
+    if constexpr (BITS == 4) {
+        // packed 4-bit weights: the tcgen05 kernel (fp32 dequantization for every M)
+        if (!force_simt && !no_bulk && !(flags & MIORI_TUNE_GEMV_MMASYNC) && (flags & MIORI_TUNE_GEMV_UMMA)) {
+            rc = gemvumma::try_launch(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
+            if (rc <= 0) return rc;  // launched (0) or failed (<0); 1 = not eligible
+        }
+    }
     if (!force_simt && !(force_exact && M > 4)) {
         if (!no_bulk) {
             rc = gemvtma::try_launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
@@ -120,3 +128,13 @@ MIORI_API int miori_device_error_poll(void) {
          rec[1], rec[2], rec[3]);
     return (int)rec[0];
 }
+
+#ifdef MIORI_UMMA_TRACE
+// Profiling build only: read and clear the tcgen05 GEMV's cycle counters.
+MIORI_API int miori_debug_umma_trace(long long* out32) {
+    long long zero[32] = {};
+    if (cudaMemcpyFromSymbol(out32, gemvumma::g_umma_trace, sizeof(zero)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(gemvumma::g_umma_trace, zero, sizeof(zero));
+    return 0;
+}
+#endif

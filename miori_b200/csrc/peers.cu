@@ -54,6 +54,18 @@ allgather_kernel(const PeerArgs pa, const uint8_t* __restrict__ src, uint32_t sr
     if (threadIdx.x == 0) peer_finish(pa, e);
 }
 
+// The limit of the kernels' waits for a peer, kept in the control block in SM clock cycles.
+static int write_wait_limit(const miori_peers* g, double microseconds) {
+    int dev = 0, khz = 0;
+    MIORI_CUDA(cudaGetDevice(&dev));
+    MIORI_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+    if (khz <= 0) khz = 1965000;
+    long long cycles = (long long)(microseconds * 1e-3 * (double)khz);
+    if (cycles < 1000) cycles = 1000;
+    MIORI_CUDA(cudaMemcpy(g->mapped[g->rank] + CTL_LIMIT * 4, &cycles, sizeof(cycles), cudaMemcpyHostToDevice));
+    return MIORI_OK;
+}
+
 // The table of mapped arenas the kernels read, in the local control block.
 static int write_table(const miori_peers* g) {
     uint8_t* table[MAX_PEERS] = {};
@@ -149,6 +161,7 @@ MIORI_API int miori_peers_create(int rank, int world, size_t arena_bytes, miori_
     }
     g->mapped[rank] = static_cast<uint8_t*>(p);
     int rc = peers::write_table(g);
+    if (rc == MIORI_OK) rc = peers::write_wait_limit(g, 1.0e6);
     if (rc) {
         cudaFree(p);
         delete g;
@@ -156,6 +169,13 @@ MIORI_API int miori_peers_create(int rank, int world, size_t arena_bytes, miori_
     }
     *out = g;
     return MIORI_OK;
+}
+
+MIORI_API int miori_peers_set_wait_us(miori_peers* g, uint32_t microseconds) {
+    if (!g) return fail(MIORI_E_INVALID, "miori_peers_set_wait_us: null peer group");
+    if (microseconds == 0 || microseconds > 10000000u)
+        return fail(MIORI_E_INVALID, "miori_peers_set_wait_us: %u us outside 1 us .. 10 s", microseconds);
+    return peers::write_wait_limit(g, (double)microseconds);
 }
 
 MIORI_API size_t miori_peers_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }

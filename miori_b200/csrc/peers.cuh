@@ -18,7 +18,7 @@
 // launch number's parity: a rank can be at most one launch ahead of a peer (its launch e+1
 // completes only after the peer's rows of e+1 arrived, which the peer sends after finishing e),
 // so a packet of launch e+1 never lands on a slot a peer still reads for launch e.
-// All waits are bounded (~1 s): on expiry the kernel records a device error, marks the control
+// All waits are bounded (about a second unless the host sets another limit): on expiry the kernel records a device error, marks the control
 // block and stops waiting, so a missing peer costs time but never hangs the GPU.  Only plain
 // loads and stores touch peer memory: no multicast, no TMA.
 #pragma once
@@ -30,7 +30,7 @@ constexpr int MAX_PEERS = 8;
 constexpr size_t PEER_CTL_BYTES = 256;      // control block at the start of every arena
 constexpr size_t PEER_TABLE_OFFSET = 128;   // MAX_PEERS arena pointers inside the control block
 constexpr size_t PEER_INBOX_FACTOR = 4;     // one inbox = 4 x user bytes: 8-byte packets for 2-byte elements
-enum : uint32_t { CTL_COUNT = 16, CTL_EPOCH = 17, CTL_ERR = 18 };
+enum : uint32_t { CTL_COUNT = 16, CTL_EPOCH = 17, CTL_ERR = 18, CTL_LIMIT = 20 /* 64-bit: wait limit in cycles */ };
 
 struct PeerArgs {          // by value in kernel parameters
     uint8_t* local;        // this rank's arena; its control block holds, at PEER_TABLE_OFFSET,
@@ -65,22 +65,34 @@ __device__ __forceinline__ uint2* peer_slot(const PeerArgs& pa, uint8_t* arena, 
     uint8_t* inbox = arena + PEER_CTL_BYTES + pa.user_bytes * (1u + (e & 1u) * PEER_INBOX_FACTOR);
     return reinterpret_cast<uint2*>(inbox) + elem;
 }
-// One element to one peer: value bits and launch number in a single 8-byte store.
+// One element to one peer: value bits (low word) and launch number (high word) as ONE 64-bit
+// store.  A scalar 8-byte access is single-copy atomic in the PTX memory model, so a reader sees
+// either the whole old packet or the whole new one; a vector store of two words would not
+// promise that.
 __device__ __forceinline__ void peer_send(uint2* slot, uint32_t bits, uint32_t e) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot), "r"(bits), "r"(e) : "memory");
+    const uint64_t pkt = (uint64_t)bits | ((uint64_t)e << 32);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(slot), "l"(pkt) : "memory");
+}
+__device__ __forceinline__ uint64_t peer_load(const uint2* slot) {
+    uint64_t pkt;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(pkt) : "l"(slot) : "memory");
+    return pkt;
 }
 // Bounded wait for the packet of launch e in a local slot; false if it never came.
 __device__ __forceinline__ bool peer_recv(const PeerArgs& pa, const uint2* slot, uint32_t e, uint32_t& bits) {
-    uint32_t got;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(got) : "l"(slot) : "memory");
-    if (got == e) return true;
+    uint64_t pkt = peer_load(slot);
+    bits = (uint32_t)pkt;
+    if ((uint32_t)(pkt >> 32) == e) return true;
     uint32_t* ctl = peer_ctl(pa);
+    // the limit is a field of the control block (miori_peers_set_wait_us; about a second by default)
+    const long long limit = *reinterpret_cast<const volatile long long*>(ctl + CTL_LIMIT);
     const long long t0 = clock64();
     for (;;) {
-        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(got) : "l"(slot) : "memory");
-        if (got == e) return true;
+        pkt = peer_load(slot);
+        bits = (uint32_t)pkt;
+        if ((uint32_t)(pkt >> 32) == e) return true;
         if (ld_relaxed_sys(ctl + CTL_ERR) != 0u) return false;  // someone already gave up
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             st_relaxed_sys(ctl + CTL_ERR, 0x7E30u);
             device_error(0x7E30u, blockIdx.x, e);
             return false;

@@ -57,11 +57,36 @@ def test_static_scratch_matches_workspace_entry_twice(M, N, K):
 def test_shape_without_split_runs_and_oversized_split_is_refused():
     A, cache = _problem(300, 256, 128, seed=9)  # too short a K to split: no scratch involved
     assert torch.equal(_static(A, cache, 256), miori_b200.gemm_bf16_cache(A, cache, 256))
-    # 1024 x 2304 with a very long K has 36 pair tiles for 74 SM pairs, so it splits K in two:
-    # 2 x 9 MiB of partials, more than the built-in 16 MiB.  The entry refuses before touching
-    # any pointer.
+    # 1024 x 2304 with a very long K has few tiles for the SMs, so it wants to split K, and two
+    # slices of 9 MiB are more than the built-in 16 MiB.  Whether it splits is the planner's
+    # decision, so ask first (host-only) and use real operands: if the plan ever changes, the call
+    # computes a product instead of being refused -- a failed assertion, never a bad address.
     M, N, K = 1024, 2304, 32768
-    rc = lib.miori_gemm_bf16_cache_static(0x1000, 0x1000, 0x1000, M, N, K, 0, None)
+    if lib.miori_gemm_workspace_bytes(M, N, K) <= lib.miori_gemm_static_scratch_bytes():
+        pytest.skip("the planner no longer wants more scratch than the built-in array for this shape")
+    A = torch.zeros((M, K), dtype=torch.bfloat16, device=DEV)
+    cache = torch.zeros((N, K), dtype=torch.bfloat16, device=DEV)
+    out = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    rc = lib.miori_gemm_bf16_cache_static(A.data_ptr(), cache.data_ptr(), out.data_ptr(), M, N, K, 0,
+                                          torch.cuda.current_stream().cuda_stream)
     assert rc == -1
     msg = lib.miori_last_error().decode()
-    assert "scratch" in msg and "miori_gemm_bf16_cache_ws" in msg and str(16 << 20) in msg
+    assert "scratch" in msg and "miori_gemm_bf16_cache " in msg and str(16 << 20) in msg
+
+
+def test_static_entry_allocates_nothing():
+    """Free device memory is the same before and after a call that uses the built-in scratch."""
+    M, N, K = 32, 2048, 2048
+    A, cache = _problem(M, N, K, seed=77)
+    assert lib.miori_gemm_workspace_bytes(M, N, K) > 0  # the shape does use scratch
+    out = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    # the first call on a device looks the array's address up; measure around a later one
+    check(lib.miori_gemm_bf16_cache_static(A.data_ptr(), cache.data_ptr(), out.data_ptr(), M, N, K, 0, st))
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        check(lib.miori_gemm_bf16_cache_static(A.data_ptr(), cache.data_ptr(), out.data_ptr(), M, N, K, 0, st))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"free device memory changed by {free0 - free1} bytes across the calls"
