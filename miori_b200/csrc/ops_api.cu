@@ -34,12 +34,10 @@ int gemv_entry(const char* op, const void* q, const void* s, const void* b, cons
     const bool force_exact = (flags & MIORI_GEMV_EXACT) != 0;
     const bool force_simt = (flags & MIORI_TUNE_GEMV_SIMT) != 0;  // tuning override: shape-agnostic SIMT path
     const bool no_bulk = (flags & MIORI_TUNE_GEMV_LDG) != 0;     // tuning override: register-streaming kernel
-    if constexpr (BITS == 4) {
-        // packed 4-bit weights: the tcgen05 kernel (fp32 dequantization for every M)
-        if (!force_simt && !no_bulk && !(flags & MIORI_TUNE_GEMV_MMASYNC) && (flags & MIORI_TUNE_GEMV_UMMA)) {
-            rc = gemvumma::try_launch(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
-            if (rc <= 0) return rc;  // launched (0) or failed (<0); 1 = not eligible
-        }
+    // the tcgen05 kernel (integer tensor cores, fp32 dequantization for every M)
+    if (!force_simt && !no_bulk && !(flags & MIORI_TUNE_GEMV_MMASYNC) && (flags & MIORI_TUNE_GEMV_UMMA)) {
+        rc = gemvumma::try_launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
+        if (rc <= 0) return rc;  // launched (0) or failed (<0); 1 = not eligible
     }
     if (!force_simt && !(force_exact && M > 4)) {
         if (!no_bulk) {
@@ -136,5 +134,8 @@ MIORI_API int miori_debug_umma_trace(long long* out32) {
     if (cudaMemcpyFromSymbol(out32, gemvumma::g_umma_trace, sizeof(zero)) != cudaSuccess) return -1;
     cudaMemcpyToSymbol(gemvumma::g_umma_trace, zero, sizeof(zero));
     return 0;
+}
+MIORI_API int miori_debug_umma_events(unsigned int* out1024) {
+    return cudaMemcpyFromSymbol(out1024, gemvumma::g_umma_ev, 1024 * sizeof(unsigned int)) == cudaSuccess ? 0 : -1;
 }
 #endif
