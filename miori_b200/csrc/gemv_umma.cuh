@@ -50,11 +50,10 @@ namespace miori_b200 {
 namespace gemvumma {
 
 constexpr int TILE_N = 128;     // rows per tile = TMEM lanes
-constexpr int KS = 128;         // codes per row and stage
-constexpr int A_COLS = KS / 4;  // TMEM columns of one unpacked stage (four 8-bit codes per column)
-// warp roles: 0-3 unpack, 4-7 drain, 8-9 issue, 10 TMA producer (and tensor-memory allocation)
-constexpr int WG_DRAIN = 4, WARP_ISSUE0 = 8, WARP_TMA = 10;
-constexpr int THREADS = 11 * 32;   // 352
+// warp roles: 0-7 unpack (two warpgroups taking alternate stages), 8-11 drain, 12-13 issue,
+// 14 TMA producer (and tensor-memory allocation)
+constexpr int WG_DRAIN = 8, WARP_ISSUE0 = 12, WARP_TMA = 14;
+constexpr int THREADS = 15 * 32;   // 480
 constexpr int STAGERS = 6 * 32;    // the drain and issuer warps stage x first
 constexpr int MAX_RING = 24;
 constexpr int MAX_SLOTS = 4;
@@ -65,7 +64,13 @@ template <int BITS, int MACC>
 struct Cfg {
     static constexpr int L = MACC <= 8 ? 4 : 3;                     // limbs of an activation
     static constexpr int NC = (MACC * L + 15) / 16 * 16;            // MMA N: (row, limb) columns
-    static constexpr int ROW_BYTES = KS * BITS / 8;                 // bytes of one row in a stage
+    // A stage is 128 bytes of every row: 256 four-bit or 128 eight-bit codes.  Every hand-over
+    // between the roles costs on the order of a hundred cycles (a load and a branch on it), so
+    // stages are as long as tensor memory allows.
+    static constexpr int KS = 1024 / BITS;                          // codes per row and stage
+    static constexpr int ROW_BYTES = 128;                           // bytes of one row in a stage
+    static constexpr int A_COLS = KS / 4;                           // TMEM columns of a stage (4 codes each)
+    static constexpr int MMAS = KS / 32;                            // MMAs per stage: 8 or 4
     // rows of x actually staged per 16-k block: with one activation row only 4 of the MMA's 16
     // columns carry limbs; the second group of 8 then re-reads rows 1..8 (row 8 is the zero pad)
     static constexpr int XROWS = MACC == 1 ? 8 : NC;
@@ -273,13 +278,13 @@ __host__ __device__ inline Smem smem_layout(const Geo& g) {
 }
 
 template <int BITS, int MACC>
-__global__ void __launch_bounds__(THREADS, MACC <= 8 ? 2 : 1)
+__global__ void __launch_bounds__(THREADS, MACC <= 4 ? 2 : 1)
 gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                  const __grid_constant__ CUtensorMap tmap_s,
                  const __grid_constant__ CUtensorMap tmap_b, const uint16_t* __restrict__ x,
                  void* __restrict__ y, const Geo geo) {
     using C = Cfg<BITS, MACC>;
-    constexpr uint32_t L = C::L, NC = C::NC, XBLK = C::XBLK;
+    constexpr uint32_t L = C::L, NC = C::NC, XBLK = C::XBLK, KS = C::KS, A_COLS = C::A_COLS;
     // instruction descriptor: D = s32, A = u8, B = s8, both K-major, shape 128 x NC
     constexpr uint32_t IDESC = (2u << 4) | (0u << 7) | (1u << 10) | ((NC >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -287,7 +292,9 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __shared__ __align__(8) uint64_t full_bars[MAX_RING];
     __shared__ __align__(8) uint64_t empty_bars[MAX_RING];
     __shared__ __align__(8) uint64_t sb_full[2], sb_empty[2];
-    __shared__ __align__(8) uint64_t a_ready[MAX_SLOTS], d_free[MAX_SLOTS];
+    // stage j may be issued once its A slot is filled (four unpack warps arrive) and its
+    // accumulator slot has been read back (four drain warps arrive): go[j % 4]
+    __shared__ __align__(8) uint64_t go[MAX_SLOTS];
     __shared__ __align__(8) uint64_t mma_done[MAX_SLOTS];  // stage j completes mma_done[j % 4]
     __shared__ __align__(8) uint64_t x_ready;
     __shared__ uint32_t tmem_base_slot;
@@ -297,7 +304,7 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t N = geo.N, M = geo.M, gshift = geo.gshift, kc = geo.kc, cs = geo.cs;
-    const uint32_t gps = (uint32_t)KS >> gshift;         // scale groups per stage: 2 or 4
+    const uint32_t gps = KS >> gshift;                   // scale groups per stage: 2, 4 or 8
     const uint32_t nst = kc / KS;                         // stages per tile
     const uint32_t d_cols = gps * NC;                     // accumulator columns of one stage
     const uint32_t rank = cs > 1u ? blockIdx.x % cs : 0u; // CTA rank in its cluster = K split
@@ -317,16 +324,15 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         abort_flag = 0u;
         for (uint32_t i = 0; i < geo.ring; ++i) {
             mbar_init(smem_addr(&full_bars[i]), 1);
-            mbar_init(smem_addr(&empty_bars[i]), 4);
+            mbar_init(smem_addr(&empty_bars[i]), sps >= 2u ? 8u : 4u);  // every unpack warp that reads the slab
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sb_full[i]), 1);
             mbar_init(smem_addr(&sb_empty[i]), 4);
         }
         for (int i = 0; i < MAX_SLOTS; ++i) {
-            mbar_init(smem_addr(&a_ready[i]), 4);
+            mbar_init(smem_addr(&go[i]), 8);
             mbar_init(smem_addr(&mma_done[i]), 2);
-            mbar_init(smem_addr(&d_free[i]), 4);
         }
         mbar_init(smem_addr(&x_ready), STAGERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -388,14 +394,18 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // ---- unpack warpgroup: thread = output row of the tile = TMEM lane.  Packed codes of the
         // stage -> one byte per code -> A slot.  A 4-bit word (codes n0..n7) becomes the two
         // columns (n0,n2,n4,n6) and (n1,n3,n5,n7); x is staged in the same order.
-        const uint32_t r = warp * 32u + lane;
-        const uint32_t t_lane = tmem_base + ((warp * 32u) << 16);
+        const uint32_t ug = warp >> 2, quad = warp & 3u;  // unpack warpgroup; TMEM lane quarter
+        const uint32_t r = quad * 32u + lane;
+        const uint32_t t_lane = tmem_base + ((quad * 32u) << 16);
         const uint32_t q_row = r * slab_pitch;
-        bool ok = true;
-        uint32_t ring = 0, ring_par = 0, half = 0, sa = 0;
-        for (uint32_t j = 0; j < total_stages; ++j) {
+        bool ok = true, new_slab = true;
+        // stage j of the CTA lives in slab j / sps (ring slot `ring`), part j % sps (`half`)
+        uint32_t ring = 0, ring_par = 0, half = ug, sa = ug;
+        while (half >= sps) { half -= sps; if (++ring == geo.ring) { ring = 0; ring_par ^= 1u; } }
+        if (sa >= geo.na) sa -= geo.na;
+        for (uint32_t j = ug; j < total_stages; j += 2u) {
             UMMA_T0(tf);
-            if (ok && half == 0u) ok = warp_wait(smem_addr(&full_bars[ring]), ring_par, &abort_flag, 0x48, lane);
+            if (ok && new_slab) ok = warp_wait(smem_addr(&full_bars[ring]), ring_par, &abort_flag, 0x48, lane);
             if (warp == 0) { UMMA_ADD(6, tf); UMMA_EV(0, j); }
             UMMA_T0(ta);
             // the MMAs that read this A slot last (stage j - na) must have completed
@@ -408,17 +418,20 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint32_t st = base + Ls.ring + ring * slab_bytes + q_row + half * (uint32_t)C::ROW_BYTES;
             const uint32_t a_t = t_lane + sa * A_COLS;
             if constexpr (BITS == 4) {
-                uint4 w[4];
 #pragma unroll
-                for (uint32_t c = 0; c < 4u; ++c) w[c] = lds_v4(st + (c << 4));
+                for (uint32_t c4 = 0; c4 < 8u; c4 += 4u) {
+                    uint4 w[4];
 #pragma unroll
-                for (uint32_t c = 0; c < 4u; ++c) {
-                    uint32_t o[8];
-                    o[0] = w[c].x & 0x0F0F0F0Fu; o[1] = (w[c].x >> 4) & 0x0F0F0F0Fu;
-                    o[2] = w[c].y & 0x0F0F0F0Fu; o[3] = (w[c].y >> 4) & 0x0F0F0F0Fu;
-                    o[4] = w[c].z & 0x0F0F0F0Fu; o[5] = (w[c].z >> 4) & 0x0F0F0F0Fu;
-                    o[6] = w[c].w & 0x0F0F0F0Fu; o[7] = (w[c].w >> 4) & 0x0F0F0F0Fu;
-                    tmem_st<8>(a_t + c * 8u, o);
+                    for (uint32_t c = 0; c < 4u; ++c) w[c] = lds_v4(st + ((c4 + c) << 4));
+#pragma unroll
+                    for (uint32_t c = 0; c < 4u; ++c) {
+                        uint32_t o[8];
+                        o[0] = w[c].x & 0x0F0F0F0Fu; o[1] = (w[c].x >> 4) & 0x0F0F0F0Fu;
+                        o[2] = w[c].y & 0x0F0F0F0Fu; o[3] = (w[c].y >> 4) & 0x0F0F0F0Fu;
+                        o[4] = w[c].z & 0x0F0F0F0Fu; o[5] = (w[c].z >> 4) & 0x0F0F0F0Fu;
+                        o[6] = w[c].w & 0x0F0F0F0Fu; o[7] = (w[c].w >> 4) & 0x0F0F0F0Fu;
+                        tmem_st<8>(a_t + (c4 + c) * 8u, o);
+                    }
                 }
             } else {
 #pragma unroll
@@ -436,14 +449,19 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
+            const bool last_here = half + 2u >= sps;  // this warpgroup's last stage inside the slab
             if (lane == 0) {
-                mbar_arrive(smem_addr(&a_ready[sa]));
-                if (half == sps - 1u) mbar_arrive(smem_addr(&empty_bars[ring]));
+                mbar_arrive(smem_addr(&go[j & 3u]));
+                if (last_here) mbar_arrive(smem_addr(&empty_bars[ring]));
             }
             if (warp == 0) { UMMA_ADD(7, tu); UMMA_EV(2, j); }
-            if (++sa == geo.na) sa = 0;
-            if (++half == sps) {
-                half = 0;
+            sa += 2u;
+            if (sa >= geo.na) sa -= geo.na;
+            half += 2u;
+            new_slab = false;
+            while (half >= sps) {
+                half -= sps;
+                new_slab = true;
                 if (++ring == geo.ring) { ring = 0; ring_par ^= 1u; }
             }
         }
@@ -535,35 +553,34 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         bool ok = warp_wait(smem_addr(&x_ready), 0u, &abort_flag, 0x43, lane);
 
         if (warp >= WARP_ISSUE0) {
-            // ---- issuers: warp h issues MMAs 2h and 2h+1 of every stage.  With group 64 those are
-            // the two halves of scale group h, with group 32 the groups 2h and 2h+1: an accumulator
-            // is only ever written by one warp, in k order.
+            // ---- issuers: warp h issues the first or the second half of every stage's MMAs.  A scale
+            // group is one or two consecutive MMAs and never straddles the halves: an accumulator is
+            // only ever written by one warp, in k order.
             const uint32_t h = warp - WARP_ISSUE0;
-            const uint32_t pg_shift = gps == 2u ? 1u : 0u;  // MMAs per scale group: 2 or 1
-            uint32_t sa = 0, sa_par = 0, sd = 0, sd_par = 1u, it = 0;
+            // MMAs per scale group: group / 32 = 2 or 1; their log2
+            const uint32_t pg_shift = gshift - 5u;
+            uint32_t sa = 0, sd = 0, it = 0;
             for (uint32_t j = 0; j < total_stages && ok; ++j) {
                 UMMA_T0(tw);
-                ok = warp_wait(smem_addr(&a_ready[sa]), sa_par, &abort_flag, 0x44, lane);
-                // the accumulator slot's previous contents (stage j - nd) must have been read back
-                if (ok && j >= geo.nd) ok = warp_wait(smem_addr(&d_free[sd]), sd_par, &abort_flag, 0x4A, lane);
+                ok = warp_wait(smem_addr(&go[j & 3u]), (j >> 2) & 1u, &abort_flag, 0x44, lane);
                 if (h == 0) { UMMA_ADD(1, tw); UMMA_EV(3, j); }
                 if (!ok) break;
                 UMMA_T0(ti0);
                 tc_fence_after();
                 const uint32_t a_t = tmem_base + sa * A_COLS;
                 const uint32_t d_t = tmem_d0 + sd * d_cols;
-                const uint32_t xb = xs + it * 8u * XBLK;  // 8 blocks of 16 k per stage
+                const uint32_t xb = xs + it * (KS / 16u) * XBLK;  // KS / 16 blocks of 16 k per stage
 #pragma unroll
-                for (uint32_t jj = 0; jj < 2u; ++jj) {
-                    const uint32_t q = h * 2u + jj;
+                for (uint32_t jj = 0; jj < (uint32_t)C::MMAS / 2u; ++jj) {
+                    const uint32_t q = h * ((uint32_t)C::MMAS / 2u) + jj;
                     const uint64_t bdesc = smem_desc_kmajor(xb + q * 2u * XBLK, XBLK, (uint32_t)C::XSBO);
                     umma_i8_elect(d_t + (q >> pg_shift) * NC, a_t + q * 8u, bdesc, IDESC,
                                   q & ((1u << pg_shift) - 1u));
                 }
                 umma_arrive_elect(smem_addr(&mma_done[j & 3u]));
                 if (h == 0) { UMMA_ADD(2, ti0); UMMA_EV(4, j); }
-                if (++sa == geo.na) { sa = 0; sa_par ^= 1u; }
-                if (++sd == geo.nd) { sd = 0; sd_par ^= 1u; }
+                if (++sa == geo.na) sa = 0;
+                if (++sd == geo.nd) sd = 0;
                 if (++it == nst) it = 0;
             }
         } else {
@@ -583,6 +600,9 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
             for (int m = 0; m < MACC; ++m) accs[m] = accb[m] = 0.0f;
             uint32_t j = 0, sd = 0;
+            // the first nd stages find their accumulator slots free
+            if (lane == 0)
+                for (uint32_t z = 0; z < geo.nd && z < total_stages; ++z) mbar_arrive(smem_addr(&go[z & 3u]));
             for (uint32_t ti = 0; ti < my_tiles; ++ti) {
                 const uint32_t tile = cluster + ti * nclusters, sbuf = geo.sb_bufs == 2u ? (ti & 1u) : 0u;
                 if (ok) ok = warp_wait(smem_addr(&sb_full[sbuf]), (geo.sb_bufs == 2u ? (ti >> 1) : ti) & 1u, &abort_flag, 0x47, lane);
@@ -593,25 +613,21 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if (!ok) break;
                     UMMA_T0(td);
                     tc_fence_after();
-                    // this row's scales and biases of the stage: gps consecutive bf16 each
-                    const uint32_t off = (sb_first + it * gps) * 2u;
-                    const uint32_t sa = base + Ls.sb + sbuf * 2u * sb_bytes + r * sb_pitch +
-                                        (((off >> 4) ^ sb_swz) << 4) + (off & 15u);
-                    uint32_t sw0, sw1 = 0u, bw0, bw1 = 0u;
-                    if (gps == 2u) {
-                        sw0 = lds_u32(sa);
-                        bw0 = lds_u32(sa + sb_bytes);
-                    } else {
-                        const uint2 s2 = lds_v2(sa), b2 = lds_v2(sa + sb_bytes);
-                        sw0 = s2.x; sw1 = s2.y; bw0 = b2.x; bw1 = b2.y;
-                    }
+                    // this row's scales and biases of the stage: gps consecutive bf16 each, read one by
+                    // one (the row's first scale need not sit on a 16-byte boundary when K is split)
+                    const uint32_t sb_row = base + Ls.sb + sbuf * 2u * sb_bytes + r * sb_pitch;
+                    const uint32_t e0 = sb_first + it * gps;
                     const uint32_t xsa = base + Ls.xsum + it * gps * MACC * 4u;
                     const uint32_t d_t = t_lane + sd * d_cols;
                     // scale and bias of group gq of the stage
                     auto group_sb = [&](uint32_t gq, float& sc, float& bi) {
-                        const uint32_t sw = gq < 2u ? sw0 : sw1, bw = gq < 2u ? bw0 : bw1;
-                        sc = bf16_bits_to_float((gq & 1u) ? (sw >> 16) : (sw & 0xFFFFu));
-                        bi = bf16_bits_to_float((gq & 1u) ? (bw >> 16) : (bw & 0xFFFFu));
+                        const uint32_t off = (e0 + gq) * 2u;
+                        const uint32_t a = sb_row + (((off >> 4) ^ sb_swz) << 4) + (off & 15u);
+                        uint32_t s16, b16;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(s16) : "r"(a));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(b16) : "r"(a + sb_bytes));
+                        sc = bf16_bits_to_float(s16);
+                        bi = bf16_bits_to_float(b16);
                     };
                     // rows mb .. mb + MB - 1 of group gq from their MB * L accumulator columns
                     auto apply = [&](uint32_t gq, int mb, int MB, const uint32_t* dv, float sc, float bi) {
@@ -627,13 +643,13 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     };
                     if constexpr (MACC == 1) {
                         // few columns: every group's accumulators in flight at once
-                        uint32_t dv[4][MACC * L];
+                        uint32_t dv[8][MACC * L];
 #pragma unroll
-                        for (uint32_t gq = 0; gq < 4u; ++gq)
+                        for (uint32_t gq = 0; gq < 8u; ++gq)
                             if (gq < gps) tmem_ld<MACC * L>(d_t + gq * NC, dv[gq]);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (uint32_t gq = 0; gq < 4u; ++gq) {
+                        for (uint32_t gq = 0; gq < 8u; ++gq) {
                             if (gq < gps) {
                                 float sc, bi;
                                 group_sb(gq, sc, bi);
@@ -657,7 +673,8 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_addr(&d_free[sd]));
+                    // the slot is free for stage j + nd
+                    if (lane == 0 && j + geo.nd < total_stages) mbar_arrive(smem_addr(&go[(j + geo.nd) & 3u]));
                     if (dw == 0) { UMMA_ADD(5, td); UMMA_EV(6, j); }
                     if (++sd == geo.nd) sd = 0;
                 }
@@ -767,7 +784,7 @@ inline Geo plan(uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t fla
     const uint32_t sms = (uint32_t)sm_count();
     const uint32_t tiles_plan = (n_plan + TILE_N - 1) / TILE_N;
     const uint32_t tiles = (N + TILE_N - 1) / TILE_N;
-    const uint32_t gps = KS / group;
+    const uint32_t gps = C::KS / group;
     const bool compact = MACC <= 8;
     // K split: double the CTAs per cluster while every CTA still gets an SM of its own and keeps
     // at least 256 codes per row.  The split is a function of the shape and of the class of M
@@ -788,9 +805,8 @@ inline Geo plan(uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t fla
         const uint32_t per_cta = g.kc / group;
         const uint32_t lead = (cs > 1u && per_cta % 8u != 0u) ? 7u : 0u;
         g.sb_box = (per_cta + lead + 7u) / 8u * 8u;
-        g.clusters = cs > 1u ? tiles : std::min<uint32_t>(tiles, (compact && tiles >= 4u * sms) ? 2u * sms : sms);
-        const uint32_t tiles_cta = (tiles + g.clusters - 1) / g.clusters;
-        g.sb_bufs = tiles_cta > 1u ? 2u : 1u;
+        g.clusters = cs > 1u ? tiles : std::min<uint32_t>(tiles, sms);
+        g.sb_bufs = tiles > g.clusters ? 2u : 1u;
         g.ring = 2;
         // slab rows: 256 bytes when the CTA's share of a row divides into them, else 128
         g.slab_row = (g.kc * BITS / 8u) % 256u == 0u ? 256u : 128u;
@@ -801,6 +817,7 @@ inline Geo plan(uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t fla
     // tensor memory: A slots of 32 columns, accumulator slots of gps * NC columns.  Half of it
     // (256 columns) when that leaves two accumulator slots, so that two CTAs can share an SM.
     const uint32_t d_cols = gps * C::NC;
+    constexpr uint32_t A_COLS = C::A_COLS;
     uint32_t cols = 256;
     if (!compact || 2u * A_COLS + 2u * d_cols > 256u) cols = 512;
     if (2u * A_COLS + d_cols > cols) { g.cs = 0; return g; }
@@ -808,14 +825,34 @@ inline Geo plan(uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t fla
     while (g.na > 2u && g.na * A_COLS + 2u * d_cols > cols) --g.na;
     g.nd = std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)MAX_SLOTS, (cols - g.na * A_COLS) / d_cols));
     g.tmem_cols = cols;
-    // ring: what shared memory allows (half an SM for the compact instantiations when four stages
-    // fit there), at most what the CTA will ever stream
+    // ring: what shared memory allows, at most what the CTA will ever stream.  The compact
+    // instantiations take half an SM when two slabs fit there, so that two CTAs share an SM: the
+    // next kernel of a dependent-launch chain beside this one, or, for long streams, two CTAs of
+    // this kernel (the grid then has two CTAs per SM).
+    const size_t half_sm = 110u * 1024u, whole_sm = 220u * 1024u;
+    bool halved = false;
+    // Only for 4-bit codes: with 8-bit codes, one activation row and two CTAs per SM a launch
+    // ended in a failure on a B200 whose cause reading the code has not shown, so 8-bit weights
+    // always take the whole SM.
+    if (compact && cols == 256u && BITS == 4) {
+        Geo h = g;
+        if (cs == 1u && tiles >= 4u * sms) {  // long stream: two CTAs per SM
+            h.clusters = std::min<uint32_t>(tiles, 2u * sms);
+            h.sb_bufs = 2u;
+        }
+        h.ring = 2;
+        if (smem_layout<BITS, MACC>(h).total > half_sm) h.slab_row = 128u;  // shorter slabs, same ring depth
+        if (smem_layout<BITS, MACC>(h).total <= half_sm) {
+            g = h;
+            halved = true;
+        }
+    }
+    g.ring = 2;
+    const size_t slab = (size_t)TILE_N * (g.slab_row + 16u);
+    const size_t fixed = smem_layout<BITS, MACC>(g).total - 2u * slab;
     const uint32_t nst = g.kc * BITS / 8u / g.slab_row;  // slabs per tile
     const uint32_t tiles_cta = (tiles + g.clusters - 1) / g.clusters;
-    const size_t slab = (size_t)TILE_N * (g.slab_row + 16u);
-    const size_t fixed = smem_layout<BITS, MACC>(g).total - (size_t)g.ring * slab;
-    const size_t budget = (compact && cols == 256u && fixed + 2u * slab <= 110u * 1024u) ? 110u * 1024u : 220u * 1024u;
-    uint32_t ring = (uint32_t)((budget - fixed) / slab);
+    uint32_t ring = (uint32_t)(((halved ? half_sm : whole_sm) - fixed) / slab);
     ring = std::min<uint32_t>(ring, (uint32_t)MAX_RING);
     ring = std::min<uint32_t>(ring, std::max<uint32_t>(2u, nst * tiles_cta));
     g.ring = ring;
@@ -886,7 +923,23 @@ inline int try_launch(const void* q, const void* s, const void* b, const void* x
     if (M <= 4) MIORI_UMMA_TRY(4);
     if (M <= 8) MIORI_UMMA_TRY(8);
     if (M <= 16) MIORI_UMMA_TRY(16);
-    MIORI_UMMA_TRY(32);
+    {
+        Geo g = plan<BITS, 32>(N, K, M, group, flags, pl.n_total ? pl.n_total : N);
+        if (g.cs != 0) {
+            if (pl.n_total) { g.n_total = pl.n_total; g.row0 = pl.row0; }
+            return launch_one<BITS, 32>(g, q, s, b, x, y, group, flags, stream);
+        }
+    }
+    // the 32-row instantiation does not fit tensor memory (4-bit codes with group 32): two
+    // launches of up to 16 rows each
+    {
+        const uint32_t m0 = 16u, m1 = M - 16u;
+        const size_t ypitch = (size_t)(pl.n_total ? pl.n_total : N) * ((flags & MIORI_OUT_BF16) ? 2u : 4u);
+        int rc = try_launch<BITS>(q, s, b, x, y, N, K, m0, group, flags, stream, pl);
+        if (rc != 0) return rc;
+        return try_launch<BITS>(q, s, b, static_cast<const uint16_t*>(x) + (size_t)m0 * K,
+                                static_cast<uint8_t*>(y) + m0 * ypitch, N, K, m1, group, flags, stream, pl);
+    }
 #undef MIORI_UMMA_TRY
 }
 

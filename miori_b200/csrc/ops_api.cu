@@ -34,8 +34,18 @@ int gemv_entry(const char* op, const void* q, const void* s, const void* b, cons
     const bool force_exact = (flags & MIORI_GEMV_EXACT) != 0;
     const bool force_simt = (flags & MIORI_TUNE_GEMV_SIMT) != 0;  // tuning override: shape-agnostic SIMT path
     const bool no_bulk = (flags & MIORI_TUNE_GEMV_LDG) != 0;     // tuning override: register-streaming kernel
-    // the tcgen05 kernel (integer tensor cores, fp32 dequantization for every M)
-    if (!force_simt && !no_bulk && !(flags & MIORI_TUNE_GEMV_MMASYNC) && (flags & MIORI_TUNE_GEMV_UMMA)) {
+    // The tcgen05 kernel (integer tensor cores, fp32 dequantization with an exact inner sum for
+    // every M).  By default it takes the 8-bit weights from three activation rows up: there the
+    // mma.sync kernel needs a second column set (M = 3, 4) or does not apply at all (M > 4 would
+    // fall to the multi-pass scalar kernel), and any batch wider than four rows when the caller
+    // asks for fp32 dequantization (MIORI_GEMV_EXACT), and long streams of 4-bit weights (four
+    // 128-row tiles per SM and more, up to four activation rows), where it runs two CTAs per SM
+    // and measured 14-17 % faster.  Elsewhere the mma.sync kernel with its shorter
+    // pipeline measured faster and stays the default; MIORI_TUNE_GEMV_UMMA forces this one.
+    const bool long_stream4 = BITS == 4 && M <= 4 && (N + 127u) / 128u >= 4u * (uint32_t)sm_count();
+    const bool umma_default = (BITS == 8 && M >= 3) || (force_exact && M > 4) || long_stream4;
+    if (!force_simt && !no_bulk && !(flags & MIORI_TUNE_GEMV_MMASYNC) &&
+        (umma_default || (flags & MIORI_TUNE_GEMV_UMMA))) {
         rc = gemvumma::try_launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream);
         if (rc <= 0) return rc;  // launched (0) or failed (<0); 1 = not eligible
     }

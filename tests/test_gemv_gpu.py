@@ -245,3 +245,114 @@ def test_gemv8_activation_range(port):
     alone = _run(8, q, s, b, xo[1:2].contiguous(), 64)
     assert np.array_equal(alone[0], got[1]), "a row's value depends on its neighbour"
     assert not _run(8, q, s, b, torch.zeros_like(x), 64).any()
+
+
+# ---- the tcgen05 kernel (integer tensor cores), forced with the private tuning flag ----------
+UMMA = 0x100000          # MIORI_TUNE_GEMV_UMMA (csrc/tune.h)
+SPLIT_SHIFT = 16         # MIORI_TUNE_UMMA_SPLIT_SHIFT
+
+
+@pytest.mark.parametrize("group", [32, 64])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("bits", [4, 8])
+def test_tcgen05_gemv_matches_oracle_every_m(port, bits, M, group):
+    """fp32 dequantization with an exact integer inner sum: the tight tolerance holds for every M."""
+    N, K = 1537, 2048   # not a multiple of the 128-row tile
+    q, s, b, x = _case(bits, N, K, M, group, seed=700 + M + bits)
+    want = port.gemv(bits, u32(q), u16(s), u16(b), u16(x), group)
+    got = _run(bits, q, s, b, x, group, flags=UMMA)
+    assert_close(got, want, rel_max=TOL_EXACT_PATH, what=f"tcgen05 gemv{bits} M={M} g={group}")
+
+
+@pytest.mark.parametrize("N,K,group", [(2048, 2048, 64), (16, 2048, 32), (512, 2048, 32), (6144, 2048, 32),
+                                       (2048, 7680, 32), (2048, 7680, 64), (3072, 2048, 64), (2048, 8192, 64),
+                                       (130, 256, 32), (8192, 2048, 64)])
+def test_tcgen05_gemv4_shapes(port, N, K, group):
+    """The reference model's projection shapes (config/m6.h) and the synthetic stack's, M = 1 and 4."""
+    q, s, b, x = _case(4, N, K, 4, group, seed=N + K)
+    want = port.gemv(4, u32(q), u16(s), u16(b), u16(x), group)
+    got4 = _run(4, q, s, b, x, group, flags=UMMA)
+    got1 = _run(4, q, s, b, x[:1].contiguous(), group, flags=UMMA)
+    assert_close(got4, want, rel_max=TOL_EXACT_PATH, what=f"tcgen05 gemv4 N={N} K={K} g={group} M=4")
+    assert np.array_equal(got1[0], got4[0]), "row 0 differs between M=1 and M=4"
+
+
+@pytest.mark.parametrize("split", [1, 2, 4, 8])
+@pytest.mark.parametrize("bits,M", [(4, 1), (4, 8), (8, 3), (4, 32)])
+def test_tcgen05_gemv_k_split_over_a_cluster(port, bits, M, split):
+    """K split over the CTAs of a cluster (partials meet through distributed shared memory)."""
+    N, K = 640, 2048
+    q, s, b, x = _case(bits, N, K, M, 64, seed=900 + split + M)
+    want = port.gemv(bits, u32(q), u16(s), u16(b), u16(x), 64)
+    got = _run(bits, q, s, b, x, 64, flags=UMMA | (split << SPLIT_SHIFT))
+    assert_close(got, want, rel_max=TOL_EXACT_PATH, what=f"tcgen05 gemv{bits} M={M} split={split}")
+    again = _run(bits, q, s, b, x, 64, flags=UMMA | (split << SPLIT_SHIFT))
+    assert np.array_equal(got, again), "the split sum is not reproducible"
+
+
+def test_tcgen05_rows_do_not_depend_on_m():
+    """Inside a class of M (<= 8, <= 16, <= 32) a row's value is bit-identical whatever the batch."""
+    N, K = 1024, 2048
+    q, s, b = synth.make_weight(N, K, 4, 64, seed=31)
+    x = synth.make_activation(32, K, seed=32)
+    for lo, hi in ((1, 8), (9, 16), (17, 32)):
+        full = _run(4, q, s, b, x[:hi].contiguous(), 64, flags=UMMA)
+        part = _run(4, q, s, b, x[:lo].contiguous(), 64, flags=UMMA)
+        assert np.array_equal(part, full[:lo]), f"rows differ between M={lo} and M={hi}"
+
+
+def test_tcgen05_activation_range(port):
+    """x is rounded to fixed point against its row's largest magnitude: a power-of-two factor on x
+    scales y exactly, an outlier in one row costs neither that row nor its neighbour the tight
+    tolerance, and zeros stay zeros."""
+    N, K = 1024, 2048
+    q, s, b, x = _case(4, N, K, 2, 64, seed=808)
+    y = _run(4, q, s, b, x, 64, flags=UMMA)
+    for k in (20, -30, 90):
+        xs = (x.float() * 2.0 ** k).to(torch.bfloat16)
+        ys = _run(4, q, s, b, xs, 64, flags=UMMA)
+        assert np.array_equal(ys, y * np.float32(2.0 ** k)), f"x * 2^{k}"
+    xo = x.clone()
+    xo[0, 7] = 3.0e4
+    xo[1, :] = (xo[1, :].float() * 2.0 ** -40).to(torch.bfloat16)
+    want = port.gemv(4, u32(q), u16(s), u16(b), u16(xo), 64)
+    got = _run(4, q, s, b, xo, 64, flags=UMMA)
+    assert_close(got[0], want[0], rel_max=TOL_EXACT_PATH, what="row with an outlier")
+    assert_close(got[1], want[1], rel_max=TOL_EXACT_PATH, what="quiet row next to the outlier")
+    assert not _run(4, q, s, b, torch.zeros_like(x), 64, flags=UMMA).any()
+
+
+def test_gemv8_batched_default_path_is_exact(port):
+    """Three rows and more of 8-bit weights run on the tcgen05 kernel by default (the reference's
+    gemv8_b and the four-row head of packed prefill, src/batch.cpp:596-600): tight tolerance."""
+    N, K = 4096, 2048
+    for M in (3, 4, 8, 32):
+        q, s, b, x = _case(8, N, K, M, 32, seed=60 + M)
+        want = port.gemv(8, u32(q), u16(s), u16(b), u16(x), 32)
+        assert_close(_run(8, q, s, b, x, 32), want, rel_max=TOL_EXACT_PATH, what=f"gemv8 M={M}")
+
+
+@pytest.mark.parametrize("flags", [0, UMMA])
+def test_config1_head_exact_shape(port, flags):
+    """The 8-bit head at its benchmark shape: N = 131072, K = 2048, group 64, every 997th row."""
+    N, K = 131072, 2048
+    q, s, b = synth.make_weight(N, K, 8, 64, seed=15, device=DEV)
+    x = synth.make_activation(1, K, seed=16)
+    y = OPS[8](q, s, b, x.to(DEV), group=64, flags=flags).cpu().numpy()
+    rows = np.arange(0, N, 997)
+    want = port.gemv(8, u32(q[rows]), u16(s[rows]), u16(b[rows]), u16(x), 64)
+    assert_close(y[:, rows], want, rel_max=TOL_EXACT_PATH, what="config 1 head")
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
+@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 2048), (16384, 2048), (2048, 8192)])
+def test_config2_grid_default_dispatch(port, N, K, M):
+    """Every projection shape of the synthetic decode stack at every M of the sweep, group 64,
+    through the default dispatch (whichever kernel it selects), on every 61st row."""
+    q, s, b = synth.make_weight(N, K, 4, 64, seed=N + K + M, device=DEV)
+    x = synth.make_activation(M, K, seed=M)
+    y = OPS[4](q, s, b, x.to(DEV), group=64).cpu().numpy()
+    rows = np.arange(0, N, 61)
+    want = port.gemv(4, u32(q[rows]), u16(s[rows]), u16(b[rows]), u16(x), 64)
+    tol = TOL_EXACT_PATH if M <= 4 else 1e-2
+    assert_close(y[:, rows], want, rel_max=tol, what=f"config 2 N={N} K={K} M={M}")
