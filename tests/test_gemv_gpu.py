@@ -356,3 +356,18 @@ def test_config2_grid_default_dispatch(port, N, K, M):
     want = port.gemv(4, u32(q[rows]), u16(s[rows]), u16(b[rows]), u16(x), 64)
     tol = TOL_EXACT_PATH if M <= 4 else 1e-2
     assert_close(y[:, rows], want, rel_max=tol, what=f"config 2 N={N} K={K} M={M}")
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_long_stream_gemv4_default_dispatch(port, M):
+    """A 151 MB matrix of 4-bit weights (N = 131072): the default dispatch takes the tcgen05 kernel
+    with two CTAs per SM there; every 997th row against the oracle, tight tolerance."""
+    N, K = 131072, 2048
+    q, s, b = synth.make_weight(N, K, 4, 64, seed=21, device=DEV)
+    x = synth.make_activation(M, K, seed=22)
+    y = OPS[4](q, s, b, x.to(DEV), group=64).cpu().numpy()
+    again = OPS[4](q, s, b, x.to(DEV), group=64).cpu().numpy()
+    rows = np.arange(0, N, 997)
+    want = port.gemv(4, u32(q[rows]), u16(s[rows]), u16(b[rows]), u16(x), 64)
+    assert_close(y[:, rows], want, rel_max=TOL_EXACT_PATH, what=f"long stream M={M}")
+    assert np.array_equal(y, again)
