@@ -245,6 +245,48 @@ int miori_allgather(miori_peers* g, const void* src, size_t y_offset, uint32_t M
                     uint32_t row0, uint32_t n_total, uint32_t elem_bytes, uint32_t flags,
                     void* stream);
 
+/* Greedy sampling over an N-sharded head without gathering the logits (the reference's host
+ * loop over 128000 logits, src/engine.cpp:740-747, ties to the lowest index): every rank passes
+ * the logits of its own rows (fp32, or bf16 with MIORI_OUT_BF16) and the index of its first row;
+ * the ranks exchange (value, index) pairs, two 8-byte packets per rank.  Afterwards the arena of
+ * every rank holds, at y_offset, `world` pairs [value fp32, index u32] and then the winning pair.
+ * Same launch-order contract as the *_allgather entries. */
+int miori_argmax_allreduce(miori_peers* g, const void* v, uint32_t n_local, uint32_t index0,
+                           size_t y_offset, uint32_t flags, void* stream);
+
+/* ---- the steps either side of a projection (reference src/engine.cpp:389-413, 484-502) and the
+ *      8-bit embedding gather that shares its table with the LM head. -------------------------- */
+
+/* rmsnorm (shaders/ops.metal:86-115, src/ops.h:16-18): y[r][i] = bf16(x[r][i] * rsqrt(mean_i
+ * x[r][i]^2 + eps) * gamma[i]); x fp32 [rows][n], gamma bf16 [n], y bf16 [rows][n]. */
+int miori_rmsnorm(const void* x, const void* gamma, void* y, uint32_t rows, uint32_t n, float eps,
+                  uint32_t flags, void* stream);
+/* post_norm_add (shaders/ops.metal:605-631): out = x + src * rsqrt(mean src^2 + eps) * gamma, all
+ * fp32 [rows][n] but gamma (bf16 [n]). */
+int miori_post_norm_add(const void* x, const void* src, const void* gamma, void* out, uint32_t rows,
+                        uint32_t n, float eps, uint32_t flags, void* stream);
+/* silu_mul (shaders/ops.metal:129-139, src/ops.h:23-24): out[i] = bf16(gate[i] / (1 + exp(-gate[i]))
+ * * up[i]); gate, up fp32, out bf16. */
+int miori_silu_mul(const void* gate, const void* up, void* out, size_t n, uint32_t flags, void* stream);
+/* embed8 (shaders/ops.metal:170-197, src/ops.h:35-37): out[t] = bf16 dequantization of row
+ * tokens[t] of the 8-bit table q/s/b [rows][K]; bit-exact with src/cpu_ref.h:36-45.  An id
+ * outside the table leaves its output row untouched. */
+int miori_embed8(const void* q, const void* s, const void* b, const void* tokens, void* out, uint32_t T,
+                 uint32_t rows, uint32_t K, uint32_t group, uint32_t flags, void* stream);
+/* Index (u32) and, if out_value is not NULL, value (fp32) of the largest of n elements (fp32, or
+ * bf16 with MIORI_OUT_BF16); ties go to the lowest index (src/engine.cpp:740-747). */
+int miori_argmax(const void* v, uint32_t n, uint32_t flags, void* out_index, void* out_value, void* stream);
+/* miori_gemv4 / miori_gemv8 with the RMSNorm of the activations fused into their staging:
+ * y = W * bf16(rmsnorm(x)), x fp32 [M][K], gamma bf16 [K].  Saves the norm's launch and the
+ * round trip of its output (the fusion the reference planned, docs/MILESTONES.md:87).  Runs on
+ * the tcgen05 kernel; shapes it does not take get MIORI_E_INVALID. */
+int miori_gemv4_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
+                        float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                        uint32_t flags, void* stream);
+int miori_gemv8_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
+                        float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                        uint32_t flags, void* stream);
+
 /* Non-zero if a kernel of this library recorded an internal error on the current
  * device since the last call (bounded wait expired); clears the record. */
 int miori_device_error_poll(void);

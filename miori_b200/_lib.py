@@ -64,6 +64,14 @@ _SIGS = {
     "miori_gemv4_allgather": (_i, [_p, _p, _p, _p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_gemv8_allgather": (_i, [_p, _p, _p, _p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_allgather": (_i, [_p, _p, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_argmax_allreduce": (_i, [_p, _p, _u32, _u32, _sz, _u32, _p]),
+    "miori_rmsnorm": (_i, [_p, _p, _p, _u32, _u32, C.c_float, _u32, _p]),
+    "miori_post_norm_add": (_i, [_p, _p, _p, _p, _u32, _u32, C.c_float, _u32, _p]),
+    "miori_silu_mul": (_i, [_p, _p, _p, _sz, _u32, _p]),
+    "miori_embed8": (_i, [_p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_argmax": (_i, [_p, _u32, _u32, _p, _p, _p]),
+    "miori_gemv4_rmsnorm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_gemv8_rmsnorm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_device_error_poll": (_i, []),
 }
 

@@ -246,6 +246,8 @@ struct Geo {
     uint32_t n_total;    // row pitch of y in elements (N, or the whole output when sharded)
     uint32_t row0;       // first output column of this launch inside y
     uint32_t clusters;   // clusters in the grid (host side only)
+    uint32_t norm;       // 1: x is fp32 and is RMS-normalised (times gamma) while it is staged
+    float eps;           // ... with this epsilon
 };
 
 // Shared-memory carve-up (bytes from a 1024-byte aligned base), identical on host and device.
@@ -269,8 +271,9 @@ __host__ __device__ inline Smem smem_layout(const Geo& g) {
     s.xsum = at;  // [kc >> gshift groups][MACC] fp32: sum of x over the group
     at += (g.kc >> g.gshift) * MACC * 4u;
     at = (at + 127u) & ~127u;
-    s.xinv = at;  // [32] fp32 powers of two that undo the rows' scaling, then [32] u32 row maxima
-    at += 2u * 32u * 4u;
+    s.xinv = at;  // [32] fp32 powers of two that undo the rows' scaling, [32] u32 row maxima, and for
+                  // the fused norm [32] fp32 rsqrt(mean + eps) and [32][6] partial sums of squares
+    at += (3u * 32u + 32u * 6u) * 4u;
     s.recv = at;  // [cs][128 / cs rows][MACC] fp32: partials received from the cluster
     at += g.cs > 1u ? TILE_N * MACC * 4u : 0u;
     s.total = at + 1024u;  // slack for aligning the base
@@ -282,6 +285,7 @@ __global__ void __launch_bounds__(THREADS, MACC <= 4 ? 2 : 1)
 gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                  const __grid_constant__ CUtensorMap tmap_s,
                  const __grid_constant__ CUtensorMap tmap_b, const uint16_t* __restrict__ x,
+                 const float* __restrict__ xnorm, const uint16_t* __restrict__ gamma,
                  void* __restrict__ y, const Geo geo) {
     using C = Cfg<BITS, MACC>;
     constexpr uint32_t L = C::L, NC = C::NC, XBLK = C::XBLK, KS = C::KS, A_COLS = C::A_COLS;
@@ -486,11 +490,54 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         bar_named(2u, STAGERS);
         pdl_wait_prior();
         if (warp == WG_DRAIN) UMMA_EV(7, 62u);
+        // Fused RMSNorm (shaders/ops.metal:86-115): the activations arrive as fp32; the CTA adds up
+        // the squares of each WHOLE row (whatever slice of K it multiplies) in a fixed order, and a
+        // unit is then read as bf16(x * rsqrt(mean + eps) * gamma), the value the stand-alone norm
+        // would have written for the GEMV to read.
+        const uint32_t rinv_a = xmax_a + 32u * 4u;  // [32] fp32: rsqrt(mean(x^2) + eps) per row
+        if (geo.norm) {
+            const uint32_t part_a = rinv_a + 32u * 4u;  // [32 rows][6 warps] partial sums
+            const uint32_t sw = st >> 5;
+            for (uint32_t m = 0; m < M; ++m) {
+                float ss = 0.0f;
+                const float4* row = reinterpret_cast<const float4*>(xnorm + (size_t)m * geo.K);
+                for (uint32_t i = st; i < geo.K / 4u; i += STAGERS) {
+                    const float4 v = __ldg(row + i);
+                    ss = __fmaf_rn(v.x, v.x, ss); ss = __fmaf_rn(v.y, v.y, ss);
+                    ss = __fmaf_rn(v.z, v.z, ss); ss = __fmaf_rn(v.w, v.w, ss);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                if (lane == 0) sts_f32(part_a + (m * 6u + sw) * 4u, ss);
+            }
+            bar_named(2u, STAGERS);
+            if (st < M) {
+                float tot = 0.0f;
+#pragma unroll
+                for (uint32_t w6 = 0; w6 < 6u; ++w6) tot += lds_f32(part_a + (st * 6u + w6) * 4u);
+                sts_f32(rinv_a + st * 4u, rsqrtf(tot / (float)geo.K + geo.eps));
+            }
+            bar_named(2u, STAGERS);
+        }
+        // one unit = 8 consecutive activations of row m as bf16 pairs
+        auto load_unit = [&](uint32_t m, uint32_t u) -> uint4 {
+            if (!geo.norm) return __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * geo.K + k0) + u);
+            const float4* p = reinterpret_cast<const float4*>(xnorm + (size_t)m * geo.K + k0 + u * 8u);
+            const float4 a = __ldg(p), b4 = __ldg(p + 1);
+            const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma + k0 + u * 8u));
+            const float inv = lds_f32(rinv_a + m * 4u);
+            uint4 o;
+            o.x = float_to_bf16_bits(a.x * inv * bf16lo(g.x)) | (float_to_bf16_bits(a.y * inv * bf16hi(g.x)) << 16);
+            o.y = float_to_bf16_bits(a.z * inv * bf16lo(g.y)) | (float_to_bf16_bits(a.w * inv * bf16hi(g.y)) << 16);
+            o.z = float_to_bf16_bits(b4.x * inv * bf16lo(g.z)) | (float_to_bf16_bits(b4.y * inv * bf16hi(g.z)) << 16);
+            o.w = float_to_bf16_bits(b4.z * inv * bf16lo(g.w)) | (float_to_bf16_bits(b4.w * inv * bf16hi(g.w)) << 16);
+            return o;
+        };
         // pass 1: the largest magnitude of every row (bf16 bit patterns order like magnitudes)
         for (uint32_t m = 0; m < M; ++m) {
             uint32_t mx = 0;
             for (uint32_t i = st; i < units; i += STAGERS) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * geo.K + k0) + i);
+                const uint4 v = load_unit(m, i);
                 const uint32_t a = v.x & 0x7FFF7FFFu, b = v.y & 0x7FFF7FFFu, c = v.z & 0x7FFF7FFFu,
                                d = v.w & 0x7FFF7FFFu;
                 mx = max(max(max(mx, a & 0xFFFFu), max(a >> 16, b & 0xFFFFu)),
@@ -507,7 +554,7 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint32_t u = u0 + lane;  // units is a multiple of 16: lane groups never straddle it
             float sum = 0.0f;
             if (u < units) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * geo.K + k0) + u);
+                const uint4 v = load_unit(m, u);
                 const uint32_t top = lds_u32(xmax_a + m * 4u);
                 // the row's largest magnitude, in [2^E, 2^(E+1)), lands in [2^(TOP_BIT-1), 2^TOP_BIT)
                 int sh = top >= 0x80u ? (int)C::TOP_BIT - 1 - ((int)(top >> 7) - 127) : 0;
@@ -766,6 +813,8 @@ gemv_umma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
 struct Placement {  // where the output goes when the launch computes a slice of a wider y
     uint32_t n_total = 0, row0 = 0;
+    const void* gamma = nullptr;  // not NULL: x is fp32 and gets the fused RMSNorm with this weight
+    float eps = 0.0f;
 };
 
 // Geometry for a problem, or cs == 0 if this kernel cannot take it.  `n_plan` is the row count
@@ -861,7 +910,7 @@ inline Geo plan(uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t fla
 
 template <int BITS, int MACC>
 inline int launch_one(const Geo& g, const void* q, const void* s, const void* b, const void* x, void* y,
-                      uint32_t group, uint32_t flags, cudaStream_t stream) {
+                      uint32_t group, uint32_t flags, cudaStream_t stream, const void* gamma = nullptr) {
     using C = Cfg<BITS, MACC>;
     CUtensorMap tq, ts, tb;
     int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)g.K * BITS / 32, g.N,
@@ -901,7 +950,10 @@ inline int launch_one(const Geo& g, const void* q, const void* s, const void* b,
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, kern, tq, ts, tb, reinterpret_cast<const uint16_t*>(x), y, g);
+    // with the fused norm x is fp32 and travels in its own parameter
+    e = cudaLaunchKernelEx(&cfg, kern, tq, ts, tb, reinterpret_cast<const uint16_t*>(g.norm ? nullptr : x),
+                           reinterpret_cast<const float*>(g.norm ? x : nullptr),
+                           reinterpret_cast<const uint16_t*>(gamma), y, g);
     if (e != cudaSuccess) return cuda_fail(e, "gemv_umma launch");
     return MIORI_OK;
 }
@@ -917,7 +969,8 @@ inline int try_launch(const void* q, const void* s, const void* b, const void* x
         Geo g = plan<BITS, MA>(N, K, M, group, flags, pl.n_total ? pl.n_total : N);         \
         if (g.cs == 0) return 1;                                                            \
         if (pl.n_total) { g.n_total = pl.n_total; g.row0 = pl.row0; }                       \
-        return launch_one<BITS, MA>(g, q, s, b, x, y, group, flags, stream);                \
+        if (pl.gamma) { g.norm = 1u; g.eps = pl.eps; }                                      \
+        return launch_one<BITS, MA>(g, q, s, b, x, y, group, flags, stream, pl.gamma);      \
     } while (0)
     if (M == 1) MIORI_UMMA_TRY(1);
     if (M <= 4) MIORI_UMMA_TRY(4);
@@ -927,7 +980,8 @@ inline int try_launch(const void* q, const void* s, const void* b, const void* x
         Geo g = plan<BITS, 32>(N, K, M, group, flags, pl.n_total ? pl.n_total : N);
         if (g.cs != 0) {
             if (pl.n_total) { g.n_total = pl.n_total; g.row0 = pl.row0; }
-            return launch_one<BITS, 32>(g, q, s, b, x, y, group, flags, stream);
+            if (pl.gamma) { g.norm = 1u; g.eps = pl.eps; }
+            return launch_one<BITS, 32>(g, q, s, b, x, y, group, flags, stream, pl.gamma);
         }
     }
     // the 32-row instantiation does not fit tensor memory (4-bit codes with group 32): two
@@ -937,8 +991,10 @@ inline int try_launch(const void* q, const void* s, const void* b, const void* x
         const size_t ypitch = (size_t)(pl.n_total ? pl.n_total : N) * ((flags & MIORI_OUT_BF16) ? 2u : 4u);
         int rc = try_launch<BITS>(q, s, b, x, y, N, K, m0, group, flags, stream, pl);
         if (rc != 0) return rc;
-        return try_launch<BITS>(q, s, b, static_cast<const uint16_t*>(x) + (size_t)m0 * K,
-                                static_cast<uint8_t*>(y) + m0 * ypitch, N, K, m1, group, flags, stream, pl);
+        const void* x1 = pl.gamma ? static_cast<const void*>(static_cast<const float*>(x) + (size_t)m0 * K)
+                                  : static_cast<const void*>(static_cast<const uint16_t*>(x) + (size_t)m0 * K);
+        return try_launch<BITS>(q, s, b, x1, static_cast<uint8_t*>(y) + m0 * ypitch, N, K, m1, group, flags,
+                                stream, pl);
     }
 #undef MIORI_UMMA_TRY
 }

@@ -4,4 +4,5 @@
 #include "backend.cu"
 #include "ops_api.cu"
 #include "gemm_tcgen05.cu"
+#include "neighbors.cu"
 #include "peers.cu"

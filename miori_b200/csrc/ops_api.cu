@@ -76,6 +76,38 @@ MIORI_API int miori_gemv8(const void* q, const void* s, const void* b, const voi
     return gemv_entry<8>("miori_gemv8", q, s, b, x, y, N, K, M, group, flags, stream);
 }
 
+namespace {
+template <int BITS>
+int gemv_rmsnorm_entry(const char* op, const void* q, const void* s, const void* b, const void* x,
+                       const void* gamma, float eps, void* y, uint32_t N, uint32_t K, uint32_t M,
+                       uint32_t group, uint32_t flags, void* stream) {
+    int rc = check_quant_args(op, q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!x || !y || !gamma) return fail(MIORI_E_INVALID, "%s: null activation, weight or output pointer", op);
+    if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
+    if (!aligned16(x) || !aligned16(gamma)) return fail(MIORI_E_INVALID, "%s: x and gamma must be 16-byte aligned", op);
+    gemvumma::Placement pl;
+    pl.gamma = gamma;
+    pl.eps = eps;
+    rc = gemvumma::try_launch<BITS>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream, pl);
+    if (rc == 1)
+        return fail(MIORI_E_INVALID, "%s: shape N=%u K=%u M=%u group=%u is outside the fused kernel's range "
+                    "(run miori_rmsnorm and the plain GEMV instead)", op, N, K, M, group);
+    return rc;
+}
+}  // namespace
+
+MIORI_API int miori_gemv4_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
+                                  float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                                  uint32_t flags, void* stream) {
+    return gemv_rmsnorm_entry<4>("miori_gemv4_rmsnorm", q, s, b, x, gamma, eps, y, N, K, M, group, flags, stream);
+}
+MIORI_API int miori_gemv8_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
+                                  float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                                  uint32_t flags, void* stream) {
+    return gemv_rmsnorm_entry<8>("miori_gemv8_rmsnorm", q, s, b, x, gamma, eps, y, N, K, M, group, flags, stream);
+}
+
 MIORI_API int miori_linear4(const void* q, const void* s, const void* b, const void* cache,
                             const void* x, void* y, uint32_t N, uint32_t K, uint32_t M,
                             uint32_t group, uint32_t flags, void* workspace, size_t workspace_bytes,

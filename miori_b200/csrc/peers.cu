@@ -54,6 +54,55 @@ allgather_kernel(const PeerArgs pa, const uint8_t* __restrict__ src, uint32_t sr
     if (threadIdx.x == 0) peer_finish(pa, e);
 }
 
+// Greedy sampling over an N-sharded head without gathering the logits: every rank finds the best
+// of its own slice, the ranks exchange (value, index) pairs -- two 8-byte packets per rank instead
+// of the whole vector -- and every rank reduces the pairs the same way (ties: lowest index, as the
+// host loop of src/engine.cpp:740-747).  One CTA.  The pairs land in the arena at y_off as
+// [rank][value, index] followed by the winner [value, index].
+template <bool BF16>
+__global__ void __launch_bounds__(1024)
+argmax_allreduce_kernel(const PeerArgs pa, const void* __restrict__ v, uint32_t n_local, uint32_t index0,
+                        size_t y_off) {
+    __shared__ neighbors::Best warp_best[32];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const neighbors::Best mine = neighbors::block_argmax<BF16>(v, n_local, index0, warp_best);
+    if (threadIdx.x == 0) {
+        uint32_t* y = reinterpret_cast<uint32_t*>(pa.local + PEER_CTL_BYTES + y_off);
+        const size_t base = y_off / 4u;
+        const uint32_t world = pa.world > 1u ? pa.world : 1u, rank = pa.world > 1u ? pa.rank : 0u;
+        y[2u * rank] = __float_as_uint(mine.v);
+        y[2u * rank + 1u] = mine.i;
+        neighbors::Best all = mine;
+        if (pa.world > 1u) {
+            const uint32_t e = peer_epoch(pa);
+            for (uint32_t p = 0; p < world; ++p) {
+                if (p == rank) continue;
+                uint8_t* arena = peer_arena(pa, p);
+                peer_send(peer_slot(pa, arena, e, base + 2u * rank), __float_as_uint(mine.v), e);
+                peer_send(peer_slot(pa, arena, e, base + 2u * rank + 1u), mine.i, e);
+            }
+            bool ok = true;
+            all = neighbors::Best{-INFINITY, 0xFFFFFFFFu};
+            for (uint32_t p = 0; p < world && ok; ++p) {
+                neighbors::Best b = mine;
+                if (p != rank) {
+                    uint32_t vb = 0, ib = 0;
+                    ok = peer_recv(pa, peer_slot(pa, pa.local, e, base + 2u * p), e, vb) &&
+                         peer_recv(pa, peer_slot(pa, pa.local, e, base + 2u * p + 1u), e, ib);
+                    b = neighbors::Best{__uint_as_float(vb), ib};
+                    y[2u * p] = vb;
+                    y[2u * p + 1u] = ib;
+                }
+                if (ok) all = neighbors::better(all, b);
+            }
+            peer_finish(pa, e);
+        }
+        y[2u * world] = __float_as_uint(all.v);
+        y[2u * world + 1u] = all.i;
+    }
+}
+
 // The limit of the kernels' waits for a peer, kept in the control block in SM clock cycles.
 static int write_wait_limit(const miori_peers* g, double microseconds) {
     int dev = 0, khz = 0;
@@ -289,5 +338,27 @@ MIORI_API int miori_allgather(miori_peers* g, const void* src, size_t y_offset, 
                    peers::peer_args(g), static_cast<const uint8_t*>(src), (uint32_t)len, y_offset, M,
                    n_total, row0, n_local);
     if (e != cudaSuccess) return cuda_fail(e, "miori_allgather launch");
+    return MIORI_OK;
+}
+
+MIORI_API int miori_argmax_allreduce(miori_peers* g, const void* v, uint32_t n_local, uint32_t index0,
+                                     size_t y_offset, uint32_t flags, void* stream) {
+    int rc = peers::check_peers("miori_argmax_allreduce", g);
+    if (rc) return rc;
+    if (!v || n_local == 0) return fail(MIORI_E_INVALID, "miori_argmax_allreduce: empty input");
+    const size_t need = (size_t)(2 * g->world + 2) * 4;
+    if (y_offset % 16 != 0 || y_offset + need > g->user_bytes)
+        return fail(MIORI_E_INVALID, "miori_argmax_allreduce: %zu bytes at offset %zu do not fit the arena", need, y_offset);
+    PeerArgs pa = peers::peer_args(g);
+    if (g->world <= 1) pa.world = 0;
+    const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
+    cudaError_t e;
+    if (flags & MIORI_OUT_BF16)
+        e = launch(peers::argmax_allreduce_kernel<true>, dim3(1), dim3(1024), 0, (cudaStream_t)stream, pdl, pa, v,
+                   n_local, index0, y_offset);
+    else
+        e = launch(peers::argmax_allreduce_kernel<false>, dim3(1), dim3(1024), 0, (cudaStream_t)stream, pdl, pa, v,
+                   n_local, index0, y_offset);
+    if (e != cudaSuccess) return cuda_fail(e, "miori_argmax_allreduce launch");
     return MIORI_OK;
 }

@@ -131,3 +131,75 @@ def linear4(q, s, b, cache, x, group=32, flags=0, out=None, workspace=None):
                             cache.data_ptr() if cache is not None else None, x.data_ptr(),
                             y.data_ptr(), N, K, M, group, flags, wp, wb, _stream()))
     return y
+
+
+def rmsnorm(x, gamma, eps, flags=0, out=None):
+    """bf16(x * rsqrt(mean(x^2) + eps) * gamma): x fp32 [rows][n], gamma bf16 [n]."""
+    _need_cuda(x, gamma)
+    rows, n = x.shape
+    y = out if out is not None else torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
+    check(lib.miori_rmsnorm(x.data_ptr(), gamma.data_ptr(), y.data_ptr(), rows, n, float(eps), flags, _stream()))
+    return y
+
+
+def post_norm_add(x, src, gamma, eps, flags=0, out=None):
+    """x + src * rsqrt(mean(src^2) + eps) * gamma, fp32 [rows][n]; gamma bf16 [n]."""
+    _need_cuda(x, src, gamma)
+    rows, n = x.shape
+    o = out if out is not None else torch.empty_like(x)
+    check(lib.miori_post_norm_add(x.data_ptr(), src.data_ptr(), gamma.data_ptr(), o.data_ptr(), rows, n,
+                                  float(eps), flags, _stream()))
+    return o
+
+
+def silu_mul(gate, up, flags=0, out=None):
+    """bf16(gate / (1 + exp(-gate)) * up), fp32 inputs of the same shape."""
+    _need_cuda(gate, up)
+    o = out if out is not None else torch.empty(gate.shape, dtype=torch.bfloat16, device=gate.device)
+    check(lib.miori_silu_mul(gate.data_ptr(), up.data_ptr(), o.data_ptr(), gate.numel(), flags, _stream()))
+    return o
+
+
+def embed8(q, s, b, tokens, group=32, flags=0, out=None):
+    """Rows tokens[t] of the 8-bit table q [rows][K/4] dequantized to bf16 [T][K]."""
+    _need_cuda(q, s, b, tokens)
+    rows, K = q.shape[0], q.shape[1] * 4
+    T = tokens.numel()
+    o = out if out is not None else torch.empty((T, K), dtype=torch.bfloat16, device=q.device)
+    check(lib.miori_embed8(q.data_ptr(), s.data_ptr(), b.data_ptr(), tokens.data_ptr(), o.data_ptr(), T, rows,
+                           K, group, flags, _stream()))
+    return o
+
+
+def argmax(v, flags=0):
+    """(index, value) tensors of the largest element of a 1-D fp32 or bf16 vector; ties: lowest index."""
+    _need_cuda(v)
+    f = flags | (OUT_BF16 if v.dtype == torch.bfloat16 else 0)
+    idx = torch.empty(1, dtype=torch.int32, device=v.device)
+    val = torch.empty(1, dtype=torch.float32, device=v.device)
+    check(lib.miori_argmax(v.data_ptr(), v.numel(), f, idx.data_ptr(), val.data_ptr(), _stream()))
+    return idx, val
+
+
+def _gemv_rmsnorm(fn, per_word, q, s, b, x, gamma, eps, group, flags, out):
+    _need_cuda(q, s, b, x, gamma)
+    if x.dtype != torch.float32:
+        raise TypeError("the fused norm takes fp32 activations")
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    M, K = x.shape
+    N = q.shape[0]
+    dt = torch.bfloat16 if flags & OUT_BF16 else torch.float32
+    y = out if out is not None else torch.empty((M, N), dtype=dt, device=x.device)
+    check(fn(q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), gamma.data_ptr(), float(eps), y.data_ptr(),
+             N, K, M, group, flags, _stream()))
+    return y
+
+
+def gemv4_rmsnorm(q, s, b, x, gamma, eps, group=32, flags=0, out=None):
+    """gemv4 over bf16(rmsnorm(x) * gamma) with the norm fused into the kernel's activation staging."""
+    return _gemv_rmsnorm(lib.miori_gemv4_rmsnorm, 8, q, s, b, x, gamma, eps, group, flags, out)
+
+
+def gemv8_rmsnorm(q, s, b, x, gamma, eps, group=32, flags=0, out=None):
+    return _gemv_rmsnorm(lib.miori_gemv8_rmsnorm, 4, q, s, b, x, gamma, eps, group, flags, out)

@@ -90,6 +90,22 @@ class PeerGroup:
         check(lib.miori_allgather(self._h, src.data_ptr(), y_offset, M, n_local, row0, n_total,
                                   src.element_size(), flags, self._stream()))
 
+    def argmax_allreduce(self, v, index0, y_offset, flags=0):
+        """Greedy pick over an N-sharded vector: v holds this rank's elements, index0 the index of
+        its first one.  Returns (index, value) read back from the arena after a synchronize."""
+        f = flags | (OUT_BF16 if v.dtype == torch.bfloat16 else 0)
+        check(lib.miori_argmax_allreduce(self._h, v.data_ptr(), v.numel(), index0, y_offset, f, self._stream()))
+
+    def argmax_result(self, y_offset):
+        """(index, value) left at y_offset by argmax_allreduce (call after synchronizing)."""
+        pairs = self.tensor(y_offset, (2 * self.world + 2,)).cpu()
+        w = 2 * self.world
+        return int(pairs[w + 1:w + 2].view(torch.int32).item()), float(pairs[w].item())
+
+    def set_wait_us(self, microseconds: int):
+        """Limit of the kernels' waits for a peer (default about a second)."""
+        check(lib.miori_peers_set_wait_us(self._h, microseconds))
+
     def status(self):
         check(lib.miori_peers_status(self._h))
 

@@ -259,5 +259,48 @@ MO_API void mo_quantize(int bits, const float* W, uint32_t* q, uint16_t* s, uint
     mo_parallel_for(0, N, quant_body, &c);
 }
 
+/*
+ * The steps either side of a projection, restated from the reference's shaders in plain
+ * fp32 as they compute them (sums of squares in double, so that the checker does not depend
+ * on a reduction order).
+ *   rmsnorm        shaders/ops.metal:86-115   y = bf16(x * rsqrt(mean(x^2) + eps) * w)
+ *   silu_mul       shaders/ops.metal:129-139  out = bf16(g / (1 + exp(-g)) * up)
+ *   post_norm_add  shaders/ops.metal:605-631  out = x + src * rsqrt(mean(src^2) + eps) * w
+ *   embed8         shaders/ops.metal:170-197  out[t][k] = bf16(code * scale + bias) of row tokens[t]
+ */
+MO_API void mo_rmsnorm(const float* x, const uint16_t* w, uint16_t* y, int64_t rows, int64_t n,
+                       float eps) {
+    for (int64_t r = 0; r < rows; ++r) {
+        double ss = 0.0;
+        for (int64_t i = 0; i < n; ++i) ss += (double)x[r * n + i] * (double)x[r * n + i];
+        const float inv = 1.0f / sqrtf((float)(ss / (double)n) + eps);
+        for (int64_t i = 0; i < n; ++i)
+            y[r * n + i] = float_to_bf16(x[r * n + i] * inv * bf16_to_float(w[i]));
+    }
+}
+MO_API void mo_silu_mul(const float* gate, const float* up, uint16_t* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        const float g = gate[i];
+        const float s = g / (1.0f + expf(-g));
+        out[i] = float_to_bf16(s * up[i]);
+    }
+}
+MO_API void mo_post_norm_add(const float* x, const float* src, const uint16_t* w, float* out,
+                             int64_t rows, int64_t n, float eps) {
+    for (int64_t r = 0; r < rows; ++r) {
+        double ss = 0.0;
+        for (int64_t i = 0; i < n; ++i) ss += (double)src[r * n + i] * (double)src[r * n + i];
+        const float inv = 1.0f / sqrtf((float)(ss / (double)n) + eps);
+        for (int64_t i = 0; i < n; ++i)
+            out[r * n + i] = x[r * n + i] + src[r * n + i] * inv * bf16_to_float(w[i]);
+    }
+}
+MO_API void mo_embed8(const uint32_t* q, const uint16_t* s, const uint16_t* b, const uint32_t* tokens,
+                      uint16_t* out, int64_t T, int64_t K, int64_t group) {
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t k = 0; k < K; ++k)
+            out[t * K + k] = float_to_bf16(dequant_elem(8, q, s, b, (int64_t)tokens[t], k, K, group));
+}
+
 MO_API int mo_num_threads(void) { return mo_threads(); }
 MO_API void mo_set_threads(int n) { g_threads = n > 0 ? (n > 256 ? 256 : n) : 0; }

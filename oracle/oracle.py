@@ -63,6 +63,10 @@ class Port:
         L.mo_gemm_bf16_entry.restype = C.c_double
         L.mo_gemm_bf16_entry.argtypes = [_pp, _pp, _i64, _i64, _i64]
         L.mo_quantize.argtypes = [C.c_int, _pp, _pp, _pp, _pp, _i64, _i64, _i64]
+        L.mo_rmsnorm.argtypes = [_pp, _pp, _pp, _i64, _i64, C.c_float]
+        L.mo_silu_mul.argtypes = [_pp, _pp, _pp, _i64]
+        L.mo_post_norm_add.argtypes = [_pp, _pp, _pp, _pp, _i64, _i64, C.c_float]
+        L.mo_embed8.argtypes = [_pp, _pp, _pp, _pp, _pp, _i64, _i64, _i64]
         L.mo_num_threads.restype = C.c_int
         L.mo_set_threads.argtypes = [C.c_int]
 
@@ -127,6 +131,35 @@ class Port:
     def gemm_entry(self, A, Bc, m, n) -> float:
         A, Bc = as_u16(A), as_u16(Bc)
         return self.lib.mo_gemm_bf16_entry(_ptr(A), _ptr(Bc), A.shape[1], m, n)
+
+    def rmsnorm(self, x, w, eps) -> np.ndarray:
+        """bf16 bits of x * rsqrt(mean(x^2) + eps) * w, x [rows][n] fp32, w [n] bf16 bits."""
+        x = np.ascontiguousarray(x, np.float32)
+        w = as_u16(w)
+        y = np.empty(x.shape, np.uint16)
+        self.lib.mo_rmsnorm(_ptr(x), _ptr(w), _ptr(y), x.shape[0], x.shape[1], eps)
+        return y
+
+    def silu_mul(self, gate, up) -> np.ndarray:
+        gate, up = np.ascontiguousarray(gate, np.float32), np.ascontiguousarray(up, np.float32)
+        out = np.empty(gate.shape, np.uint16)
+        self.lib.mo_silu_mul(_ptr(gate), _ptr(up), _ptr(out), gate.size)
+        return out
+
+    def post_norm_add(self, x, src, w, eps) -> np.ndarray:
+        x, src = np.ascontiguousarray(x, np.float32), np.ascontiguousarray(src, np.float32)
+        w = as_u16(w)
+        out = np.empty(x.shape, np.float32)
+        self.lib.mo_post_norm_add(_ptr(x), _ptr(src), _ptr(w), _ptr(out), x.shape[0], x.shape[1], eps)
+        return out
+
+    def embed8(self, q, s, b, tokens, group) -> np.ndarray:
+        q, s, b = as_u32(q), as_u16(s), as_u16(b)
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        K = q.shape[1] * 4
+        out = np.empty((tokens.size, K), np.uint16)
+        self.lib.mo_embed8(_ptr(q), _ptr(s), _ptr(b), _ptr(tokens), _ptr(out), tokens.size, K, group)
+        return out
 
     def quantize(self, bits, W, group):
         W = np.ascontiguousarray(W, np.float32)

@@ -1,0 +1,105 @@
+"""The steps either side of a projection (RMSNorm, SiLU x up, post-norm + residual), the 8-bit
+embedding gather, the arg-max, and the GEMV with the RMSNorm fused into its activation staging,
+against the CPU restatements of the reference's shaders (oracle/miori_oracle.c)."""
+import numpy as np
+import pytest
+import torch
+
+import miori_b200
+from miori_b200 import synth
+from conftest import TOL_EXACT_PATH, assert_close, u16, u32
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def bf16_ulps(a_bits, b_bits):
+    """Distance in bf16 steps between two arrays of bf16 bit patterns (same-sign finite values)."""
+    def key(v):
+        v = v.astype(np.int32)
+        return np.where(v & 0x8000, 0x8000 - (v & 0x7FFF), v + 0x8000)
+    return np.abs(key(a_bits) - key(b_bits))
+
+
+@pytest.mark.parametrize("rows,n", [(1, 2048), (4, 2048), (3, 7680), (32, 1000)])
+def test_rmsnorm(port, rows, n):
+    g = torch.Generator().manual_seed(rows + n)
+    x = torch.randn((rows, n), generator=g) * 3.0
+    w = (torch.randn(n, generator=g) * 0.2 + 1.0).to(torch.bfloat16)
+    y = miori_b200.rmsnorm(x.to(DEV), w.to(DEV), 1e-5)
+    want = port.rmsnorm(x.numpy(), u16(w), 1e-5)
+    d = bf16_ulps(u16(y), want)
+    assert d.max() <= 1, f"rmsnorm differs by {d.max()} bf16 steps"
+    assert (d != 0).mean() < 0.02   # only where fp32 rounding of the sum of squares tips a rounding
+
+
+def test_silu_mul(port):
+    g = torch.Generator().manual_seed(3)
+    gate, up = torch.randn(7680 * 3, generator=g) * 4.0, torch.randn(7680 * 3, generator=g)
+    gate[:4] = torch.tensor([0.0, -100.0, 100.0, -0.0])
+    out = miori_b200.silu_mul(gate.to(DEV), up.to(DEV))
+    d = bf16_ulps(u16(out), port.silu_mul(gate.numpy(), up.numpy()))
+    assert d.max() <= 1 and (d != 0).mean() < 0.01
+
+
+@pytest.mark.parametrize("rows,n", [(1, 2048), (5, 2048)])
+def test_post_norm_add(port, rows, n):
+    g = torch.Generator().manual_seed(rows)
+    x, src = torch.randn((rows, n), generator=g), torch.randn((rows, n), generator=g) * 2.0
+    w = (torch.randn(n, generator=g) * 0.1 + 1.0).to(torch.bfloat16)
+    out = miori_b200.post_norm_add(x.to(DEV), src.to(DEV), w.to(DEV), 1e-5)
+    want = port.post_norm_add(x.numpy(), src.numpy(), u16(w), 1e-5)
+    assert_close(out.cpu().numpy(), want, rel_max=1e-6, what="post_norm_add")
+
+
+@pytest.mark.parametrize("group", [32, 64])
+def test_embed8_bit_exact(port, group):
+    rows, K = 1000, 2048
+    q, s, b = synth.make_weight(rows, K, 8, group, seed=41)
+    tokens = torch.tensor([0, 999, 17, 17, 512, 3], dtype=torch.int32)
+    out = miori_b200.embed8(q.to(DEV), s.to(DEV), b.to(DEV), tokens.to(DEV), group=group)
+    want = port.embed8(u32(q), u16(s), u16(b), tokens.numpy().astype(np.uint32), group)
+    assert np.array_equal(u16(out), want)
+    # the same rows as the cache build produces them
+    full = miori_b200.dequant8_rowmajor(q.to(DEV), s.to(DEV), b.to(DEV), group=group)
+    assert torch.equal(out, full[tokens.long().to(DEV)])
+    # an id outside the table leaves its row as it was
+    guard = torch.full((2, K), 7.0, dtype=torch.bfloat16, device=DEV)
+    miori_b200.embed8(q.to(DEV), s.to(DEV), b.to(DEV), torch.tensor([5, 1000], dtype=torch.int32, device=DEV),
+                      group=group, out=guard)
+    assert (guard[1] == 7.0).all() and torch.equal(guard[0], full[5])
+
+
+def test_argmax_ties_go_to_the_lowest_index():
+    g = torch.Generator().manual_seed(9)
+    v = torch.randn(131072, generator=g)
+    idx, val = miori_b200.argmax(v.to(DEV))
+    assert int(idx.item()) == int(np.argmax(v.numpy())) and float(val.item()) == float(v.max())
+    v[1000] = v[77777] = v.max() + 1.0
+    idx, _ = miori_b200.argmax(v.to(DEV))
+    assert int(idx.item()) == 1000
+    vb = v.to(torch.bfloat16)
+    idx, val = miori_b200.argmax(vb.to(DEV))
+    assert int(idx.item()) == int(np.argmax(vb.float().numpy())) and float(val.item()) == float(vb.float().max())
+
+
+@pytest.mark.parametrize("bits,N,K,M,group", [(4, 2048, 2048, 1, 64), (4, 3072, 2048, 4, 32), (4, 640, 2048, 8, 64),
+                                              (8, 1024, 2048, 2, 64), (4, 2048, 8192, 1, 64), (4, 1536, 2048, 32, 64)])
+def test_gemv_with_fused_rmsnorm(port, bits, N, K, M, group):
+    """y = W * bf16(rmsnorm(x)): the fused kernel against the oracle's norm followed by its GEMV,
+    and against this library's own unfused pair."""
+    q, s, b = synth.make_weight(N, K, bits, group, seed=N + K + M)
+    g = torch.Generator().manual_seed(M)
+    x = torch.randn((M, K), generator=g) * 2.5
+    w = (torch.randn(K, generator=g) * 0.2 + 1.0).to(torch.bfloat16)
+    fused = (miori_b200.gemv4_rmsnorm if bits == 4 else miori_b200.gemv8_rmsnorm)(
+        q.to(DEV), s.to(DEV), b.to(DEV), x.to(DEV), w.to(DEV), 1e-5, group=group).cpu().numpy()
+    xn = port.rmsnorm(x.numpy(), u16(w), 1e-5)
+    want = port.gemv(bits, u32(q), u16(s), u16(b), xn, group)
+    # a bf16 rounding of a normalised activation may tip differently than in the oracle (fp32 order
+    # of the sum of squares): each such flip moves one term by 2^-8 of its size
+    assert_close(fused, want, rel_max=1e-3, what=f"fused norm gemv{bits} M={M}")
+    xn_dev = miori_b200.rmsnorm(x.to(DEV), w.to(DEV), 1e-5)
+    unfused = (miori_b200.gemv4 if bits == 4 else miori_b200.gemv8)(
+        q.to(DEV), s.to(DEV), b.to(DEV), xn_dev, group=group, flags=0x100000).cpu().numpy()
+    assert_close(fused, unfused, rel_max=1e-3, what="fused vs unfused")
