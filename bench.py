@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-matmul hot path on B200.
 
-Headline workload (BASELINE.json configs[2]): a synthetic 24-layer int4 stack, four
+Headline workload: a synthetic 24-layer int4 stack, four
 projections per layer (2048->3072, 2048->2048, 2048->16384, 8192->2048), group-64 affine
 4-bit weights, evaluated at M in {1,2,4,8,16,32} activation rows.  One "step" is one pass of
 the GEMV path over the whole stack at each of the six M values (576 GEMV launches, six
@@ -10,11 +10,15 @@ packed weight bytes streamed per step, inputs resident in HBM.  `e2e` is the sam
 with host buffers: every pass copies its activations from pinned host memory and reads the
 last layer's outputs back, all through the C ABI.
 
-`--impl reference` times the reference's CPU arithmetic (oracle/_ref when group is 32 and it
-was built, else the C port in oracle/) on the host cores on a bounded sample.
+`--impl reference` times the reference's CPU arithmetic (its own header compiled into
+oracle/_ref when present, else the C port in oracle/) on the host cores on a bounded sample, at
+every M of the sweep.
 
-With torchrun (N>1) every projection is sharded by output rows N across ranks and each GEMV
-is followed by an NCCL all-gather of y (strong scaling: the total work is fixed).
+With torchrun (N>1) the total work is fixed (strong scaling).  A projection is split by output
+rows over the ranks, its y gathered by peer stores from the GEMV's own epilogue (or by
+ncclAllGather with --allgather nccl), only when its weights are large enough for the split to
+pay (--shard policy, the default); the others are computed by every rank.  Outside the timed
+region every rank checks one forced-sharded pass against the single-GPU kernels.
 """
 from __future__ import annotations
 
@@ -221,6 +225,11 @@ def main():
     ap.add_argument("--allgather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: gather y by peer stores from the GEMV epilogue (default) or with "
                          "ncclAllGather after each launch")
+    ap.add_argument("--shard", default="policy", choices=["policy", "all", "none"],
+                    help="N > 1: which projections are split by rows over the ranks: those whose packed "
+                         "weights reach --shard-bytes (policy), all of them, or none")
+    ap.add_argument("--shard-bytes", type=int, default=16 << 20,
+                    help="policy: a projection is split when its packed weights reach this many bytes")
     ap.add_argument("--eager", action="store_true",
                     help="launch the passes directly instead of replaying CUDA graphs (for a "
                          "profiler's launch list; timings then include host launch overhead)")
@@ -255,23 +264,36 @@ def main():
     G = args.group
     pdl = 0 if args.no_pdl else miori_b200.LAUNCH_PDL
 
-    # ---- weights: every rank holds its row shard of every projection
-    stack = []
+    # ---- which projections are split by rows over the ranks
+    def is_sharded(i):
+        N, K = SHAPES[i]
+        if world == 1 or args.shard == "none":
+            return False
+        return args.shard == "all" or packed_bytes(N, K, 4, G) >= args.shard_bytes
+    sharded = [is_sharded(i) for i in range(len(SHAPES))]
+
+    def shard_rows(t, N):
+        rows = N // world
+        return t[rank * rows:(rank + 1) * rows].contiguous()
+
+    # ---- weights: the row shard of a split projection, the whole matrix of the others.  The last
+    # layer is kept in both forms on every rank for the parity check below.
+    stack, last_full, last_shard = [], [], []
     for l in range(layers):
         projs = []
         for i, (N, K) in enumerate(SHAPES):
             assert N % (16 * world) == 0
-            rows = N // world
             q, s, b = synth.make_weight(N, K, 4, G, seed=1234 + l * 4 + i, device=dev)
-            sl = slice(rank * rows, (rank + 1) * rows)
-            projs.append((q[sl].contiguous(), s[sl].contiguous(), b[sl].contiguous()))
+            if l == layers - 1 and world > 1:
+                last_full.append((q, s, b))
+                last_shard.append((shard_rows(q, N), shard_rows(s, N), shard_rows(b, N)))
+            projs.append((shard_rows(q, N), shard_rows(s, N), shard_rows(b, N)) if sharded[i] else (q, s, b))
             del q, s, b
         stack.append(projs)
     bytes_pass = layers * sum(packed_bytes(N, K, 4, G) for N, K in SHAPES)  # whole job
     say("weights ready")
-    MMAX = max(M_SWEEP)
-    # the four activations of a pass live in one device buffer, and so do its four outputs, so the
-    # end-to-end leg moves each pass's inputs and results with one copy each way
+    # the four activations of a pass live in one device buffer, so the end-to-end leg moves each
+    # pass's inputs with one copy
     def carve(flat, shapes):
         out, at = [], 0
         for shp in shapes:
@@ -284,55 +306,122 @@ def main():
     def flat_len(shapes):
         return sum((a * b + 127) // 128 * 128 for a, b in shapes)
 
-    x_flat, y_flat, x_dev, y_loc = {}, {}, {}, {}
+    x_flat, x_dev, y_loc = {}, {}, {}
     for M in M_SWEEP:
         xs = [(M, K) for _, K in SHAPES]
-        ys = [(M, N // world) for N, _ in SHAPES]
         x_flat[M] = torch.empty(flat_len(xs), dtype=torch.bfloat16, device=dev)
-        y_flat[M] = torch.empty(flat_len(ys), dtype=torch.float32, device=dev)
-        x_dev[M], y_loc[M] = carve(x_flat[M], xs), carve(y_flat[M], ys)
+        x_dev[M] = carve(x_flat[M], xs)
+        # local outputs: this rank's rows of a split projection, all rows of the others
+        y_loc[M] = [torch.empty((M, N // world if sharded[i] else N), device=dev) for i, (N, _) in enumerate(SHAPES)]
         for v, (_, K) in zip(x_dev[M], SHAPES):
             v.copy_(synth.make_activation(M, K, seed=50 + M, device=dev))
-    # N > 1: the gathered outputs.  "peer": y[M][N] at the same offset of every rank's arena,
-    # written by all ranks' GEMV epilogues over NVLink; "nccl": rank-major blocks from ncclAllGather
-    grp, y_off, gather = None, None, "none"
+    # N > 1: the gathered outputs of split projections.  "peer": y[M][N] at the same offset of every
+    # rank's arena, written by all ranks' GEMV epilogues over NVLink; "nccl": rank-major blocks
+    grp, gather = None, "none"
     if world > 1 and args.allgather == "peer":
         from miori_b200.peers import PeerGroup
         try:
-            grp = PeerGroup(rank, world, 16 << 20, dev)
+            grp = PeerGroup(rank, world, 32 << 20, dev)
             gather = "peer stores fused in the GEMV epilogue"
         except RuntimeError as e:
             say(f"peer mapping unavailable ({e}); using ncclAllGather")
-    if grp is not None:
-        y_off = {M: [grp.alloc(M * N * 4) for N, _ in SHAPES] for M in M_SWEEP}
-        y_all = {M: [grp.tensor(o, (M, N)) for o, (N, _) in zip(y_off[M], SHAPES)] for M in M_SWEEP}
-    else:
-        if world > 1:
-            gather = "ncclAllGather after each launch"
-        y_all = {M: [torch.empty((world * M, N // world), device=dev) for N, _ in SHAPES] for M in M_SWEEP}
+    if world > 1 and grp is None:
+        gather = "ncclAllGather after each launch"
+    y_off = {M: [grp.alloc(M * N * 4) if grp is not None else None for N, _ in SHAPES] for M in M_SWEEP}
+
+    def gathered(M, i):
+        """Where the whole y of projection i ends up on this rank."""
+        N = SHAPES[i][0]
+        if not sharded[i]:
+            return y_loc[M][i]
+        if grp is not None:
+            return grp.tensor(y_off[M][i], (M, N))
+        return y_nccl[M][i]
+    y_nccl = {M: [torch.empty((world * M, N // world), device=dev) if sharded[i] and grp is None else None
+                  for i, (N, _) in enumerate(SHAPES)] for M in M_SWEEP}
 
     # bf16 caches for the wide-batch path (M > 8 goes through the cache GEMM, the reference's
     # own policy for wide batches) and one split-K workspace shared by the in-order launches
     caches = [[miori_b200.dequant4_cache(q, s, b, group=G) for (q, s, b) in projs] for projs in stack]
-    ws_bytes = max(lib.miori_gemm_workspace_bytes(M, N // world, K) for M in M_SWEEP for N, K in SHAPES)
+    ws_bytes = max(lib.miori_gemm_workspace_bytes(M, N // world if sharded[i] else N, K)
+                   for M in M_SWEEP for i, (N, K) in enumerate(SHAPES))
     ws = torch.empty(max(ws_bytes // 4, 4), dtype=torch.float32, device=dev)
 
     def packed_path(M, K):  # miori_linear4's own rule
         return M <= 8 or (M <= 16 and K <= 2048)
 
+    def run_proj(M, i, w, cache, x, split):
+        """One projection: on this rank's rows with the result gathered everywhere (split), or whole."""
+        N, K = SHAPES[i]
+        q, s, b = w
+        if not split:
+            miori_b200.linear4(q, s, b, cache, x, group=G, flags=pdl, out=y_loc[M][i], workspace=ws)
+            return
+        if grp is not None and packed_path(M, K):
+            grp.gemv_allgather(4, q, s, b, x, y_off[M][i], rank * (N // world), N, group=G, flags=pdl)
+            return
+        y = y_loc[M][i] if sharded[i] else torch.empty((M, N // world), device=dev)
+        miori_b200.linear4(q, s, b, cache, x, group=G, flags=pdl, out=y, workspace=ws)
+        if grp is not None:
+            grp.allgather(y, y_off[M][i], rank * (N // world), N, flags=pdl)
+        else:
+            dist.all_gather_into_tensor(y_nccl[M][i], y)
+
     def one_pass(M):
         for projs, cs in zip(stack, caches):
-            for i, ((q, s, b), c, x, y, ya) in enumerate(zip(projs, cs, x_dev[M], y_loc[M], y_all[M])):
-                N, K = SHAPES[i]
+            for i, (w, c, x) in enumerate(zip(projs, cs, x_dev[M])):
+                run_proj(M, i, w, c, x, sharded[i])
+
+    # ---- parity of the split path (N > 1, outside every timed region): the last layer's four
+    # projections, forced through the row split at M = 1 and M = 32, against the same kernels on
+    # the unsplit weights.  The packed-weight GEMV must agree bit for bit; the cache GEMM picks its
+    # K split by shape, so its rows agree to fp32 rounding.
+    parity = None
+    if world > 1:
+        keep = (sharded, y_off)
+        cases, worst_gemm, bad = 0, 0.0, []
+        for M in (1, 32):
+            tmp_off = [grp.alloc(M * N * 4) if grp is not None else None for N, _ in SHAPES]
+            for i, (N, K) in enumerate(SHAPES):
+                full, part = last_full[i], last_shard[i]
+                x = x_dev[M][i]
+                want = miori_b200.linear4(*full, miori_b200.dequant4_cache(*full, group=G), x, group=G,
+                                          workspace=ws)
+                c_part = miori_b200.dequant4_cache(*part, group=G)
+                rows = N // world
                 if grp is not None and packed_path(M, K):
-                    grp.gemv_allgather(4, q, s, b, x, y_off[M][i], rank * (N // world), N, group=G,
-                                       flags=pdl)
-                    continue
-                miori_b200.linear4(q, s, b, c, x, group=G, flags=pdl, out=y, workspace=ws)
-                if grp is not None:
-                    grp.allgather(y, y_off[M][i], rank * (N // world), N, flags=pdl)
-                elif world > 1:
-                    dist.all_gather_into_tensor(ya, y)
+                    grp.gemv_allgather(4, *part, x, tmp_off[i], rank * rows, N, group=G, flags=pdl)
+                    torch.cuda.synchronize()
+                    got = grp.tensor(tmp_off[i], (M, N))
+                else:
+                    yp = miori_b200.linear4(*part, c_part, x, group=G, workspace=ws)
+                    if grp is not None:
+                        grp.allgather(yp, tmp_off[i], rank * rows, N, flags=pdl)
+                        torch.cuda.synchronize()
+                        got = grp.tensor(tmp_off[i], (M, N))
+                    else:
+                        buf = torch.empty((world * M, rows), device=dev)
+                        dist.all_gather_into_tensor(buf, yp)
+                        got = buf.view(world, M, rows).permute(1, 0, 2).reshape(M, N)
+                torch.cuda.synchronize()
+                cases += 1
+                if packed_path(M, K):
+                    if not torch.equal(got, want):
+                        bad.append(f"M={M} N={N} K={K}")
+                else:
+                    rel = float((got - want).abs().max() / want.abs().max())
+                    worst_gemm = max(worst_gemm, rel)
+                    if not rel <= 1e-5:
+                        bad.append(f"M={M} N={N} K={K} rel={rel:.2e}")
+        flag = torch.tensor([len(bad)], device=dev)
+        dist.all_reduce(flag)
+        parity = {"sharded_vs_single": "bit-exact" if int(flag.item()) == 0 else "MISMATCH",
+                  "cases": cases, "gemm_path_max_rel": worst_gemm, "failed": bad}
+        if int(flag.item()) != 0:
+            print(f"[bench rank {rank}] sharded path differs from the single-GPU kernels: {bad}",
+                  file=sys.stderr, flush=True)
+        del last_full, last_shard
+        say(f"parity: {parity}")
 
     # ---- capture one CUDA graph per M
     for M in M_SWEEP:
@@ -356,15 +445,21 @@ def main():
             one_pass(M)
         graphs[M] = g
     launches_pass = layers * len(SHAPES)
+    if world > 1:
+        # every rank has instantiated its graphs before anyone replays: the kernels' waits for a peer
+        # are bounded, and a rank still capturing would look like a missing one
+        torch.cuda.synchronize()
+        dist.barrier()
 
     def kernels_in_pass(M):  # this library's kernel launches in one pass at M rows, on one rank
         n = 0
-        for N, K in SHAPES:
+        for i, (N, K) in enumerate(SHAPES):
             if packed_path(M, K):
                 n += 1
                 continue
-            n += 2 if lib.miori_gemm_workspace_bytes(M, N // world, K) else 1  # GEMM (+ K-split sum)
-            n += 1 if grp is not None else 0                                      # peer all-gather
+            rows = N // world if sharded[i] else N
+            n += 2 if lib.miori_gemm_workspace_bytes(M, rows, K) else 1   # GEMM (+ K-split sum)
+            n += 1 if (grp is not None and sharded[i]) else 0             # peer all-gather
         return layers * n
     say("graphs captured")
 
@@ -396,9 +491,8 @@ def main():
     for _ in range(max(3, args.warmup)):
         step()
     if rank == 0:
-        sampler.lines.clear()  # keep only samples taken under the timed load
+        sampler.lines.clear()  # keep only samples taken under load: the timed region and all that follows
     ms_total = timed(step, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
     say(f"timed region done: {ms_step:.3f} ms/step")
     value = len(M_SWEEP) * bytes_pass / (ms_step * 1e-3) / 1e9
@@ -446,19 +540,9 @@ def main():
     host_x, host_y, dev_y = {}, {}, {}
     for M in M_SWEEP:
         host_x[M] = x_flat[M].cpu().pin_memory()
-        if world > 1 and grp is not None:   # gathered outputs: consecutive blocks of the arena
-            lo, hi = y_off[M][0], y_off[M][-1] + M * SHAPES[-1][0] * 4
-            dev_y[M] = grp.tensor(lo, ((hi - lo) // 4,))
-        elif world > 1:                      # NCCL: four separate gathered tensors
-            dev_y[M] = None
-        else:
-            dev_y[M] = y_flat[M]
-        if dev_y[M] is not None:
-            host_y[M] = torch.empty(dev_y[M].numel()).pin_memory()
-            d2h += dev_y[M].numel() * 4
-        else:
-            host_y[M] = [torch.empty((world * M, N // world)).pin_memory() for N, _ in SHAPES]
-            d2h += sum(t.numel() * 4 for t in host_y[M])
+        dev_y[M] = [gathered(M, i) for i in range(len(SHAPES))]   # the whole y of every projection
+        host_y[M] = [torch.empty(t.shape).pin_memory() for t in dev_y[M]]
+        d2h += sum(t.numel() * 4 for t in dev_y[M])
         h2d += host_x[M].numel() * 2
 
     def e2e_step():
@@ -466,12 +550,8 @@ def main():
             check(lib.miori_memcpy_h2d(x_flat[M].data_ptr(), host_x[M].data_ptr(),
                                        host_x[M].numel() * 2, stream))
             graphs[M].replay()
-            if dev_y[M] is not None:
-                check(lib.miori_memcpy_d2h(host_y[M].data_ptr(), dev_y[M].data_ptr(),
-                                           host_y[M].numel() * 4, stream))
-            else:
-                for hy, dy in zip(host_y[M], y_all[M]):
-                    check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
+            for hy, dy in zip(host_y[M], dev_y[M]):
+                check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
             check(lib.miori_stream_sync(stream))  # the host consumes this pass's result
 
     say("per-M breakdown done")
@@ -501,8 +581,13 @@ def main():
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
         "gpu_launches": args.steps * sum(kernels_in_pass(M) for M in M_SWEEP),
-        "per_m": per_m, "roofline": roofline, "clocks": clocks,
+        "per_m": per_m, "roofline": roofline,
+        "sharding": {"mode": args.shard if world > 1 else "single GPU", "threshold_bytes": args.shard_bytes,
+                     "split": [f"{K}->{N}" for (N, K), sp in zip(SHAPES, sharded) if sp],
+                     "replicated": [f"{K}->{N}" for (N, K), sp in zip(SHAPES, sharded) if not sp]},
     }
+    if parity is not None:
+        out["parity"] = parity
 
     if rank == 0 and not args.no_extras and world == 1:
         out["extras"] = extras(torch, miori_b200, synth, dev, G, peaks, timed)
@@ -515,11 +600,17 @@ def main():
         c4 = config4_prefill(torch, miori_b200, synth, dev, G, peaks, timed, rank, world)
         if rank == 0:
             out.setdefault("extras", {})["config4_prefill_gemm_m131072"] = c4
+    if rank == 0:
+        # the sampler ran through the timed region, the per-M passes, the end-to-end leg and the extras
+        out["clocks"] = sampler.stop()
     if rank == 0 and not args.no_cpu:
         out["cpu_baseline"] = cpu_decode_sample(G, seconds=12.0)
         out["cpu_baseline"].pop("seconds", None)
     if rank == 0:
         print(json.dumps(out), flush=True)
+    if parity is not None and parity["sharded_vs_single"] != "bit-exact":
+        sys.stdout.flush()
+        os._exit(3)
     if world > 1:
         # Captured graphs hold NCCL work and tearing the communicator down under them can block;
         # every rank has finished the same work here, so leave without the teardown.
@@ -536,9 +627,11 @@ def main():
 
 
 def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world, grp):
-    """BASELINE config 1 on N > 1 GPUs: the 8-bit head (N=131072, K=2048, M=1, bf16 logits) with
-    its rows split over the ranks and the logits gathered by the GEMV's own epilogue.  Every rank
-    cycles through a pool of distinct shards larger than L2; GB/s counts the whole matrix."""
+    """The 8-bit head (N=131072, K=2048, M=1, bf16 logits) with its rows split over the ranks.
+    Two ways to finish: the logits gathered on every rank by the GEMV's own epilogue, or -- for greedy
+    sampling -- only each rank's best (value, index) exchanged (two 8-byte packets per rank).  Every
+    rank cycles through a pool of distinct shards larger than L2; GB/s counts the whole matrix."""
+    import torch.distributed as dist
     N, K = 131072, 2048
     rows = N // world
     shard_bytes = packed_bytes(rows, K, 8, G)
@@ -552,22 +645,44 @@ def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world,
         pool.append((q, sc, bi))
     x = synth.make_activation(1, K, seed=9, device=dev)
     off = grp.alloc(N * 2)
+    off_best = grp.alloc(256)
+    y_local = torch.empty((1, rows), dtype=torch.bfloat16, device=dev)
     flags = miori_b200.LAUNCH_PDL | miori_b200.OUT_BF16
+    by = packed_bytes(N, K, 8, G)
 
-    def run():
+    def run_gather():
         for q, sc, bi in pool:
             grp.gemv_allgather(8, q, sc, bi, x, off, rank * rows, N, group=G, flags=flags)
-    run()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
+
+    def run_argmax():
+        for q, sc, bi in pool:
+            miori_b200.gemv8(q, sc, bi, x, group=G, flags=flags, out=y_local)
+            grp.argmax_allreduce(y_local.view(-1), rank * rows, off_best, flags=miori_b200.LAUNCH_PDL)
+
+    out = {"n_gpus": world, "rows_per_gpu": rows, "pool": npool, "out": "bf16"}
+    for name, run in (("gather_logits", run_gather), ("exchange_argmax", run_argmax)):
         run()
-    ms = timed(g.replay, 10) / 10 / npool
-    by = packed_bytes(N, K, 8, G)
-    return {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
-            "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
-            "n_gpus": world, "rows_per_gpu": rows, "pool": npool, "out": "bf16",
-            "how": "CUDA graph of dependent launches over a pool of distinct shards (> L2 per "
-                   "rank); every launch ends with the whole logits vector on every rank"}
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = timed(g.replay, 10) / 10 / npool
+        out[name] = {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
+                     "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / (world * peaks["hbm_gbs"])}
+    # the exchanged winner must be the arg-max of the gathered logits of the last matrix (ties: lowest index)
+    torch.cuda.synchronize()
+    logits = grp.tensor(off, (N,), torch.bfloat16).float()
+    want = int(torch.argmax((logits == logits.max()).to(torch.int8)).item())
+    got_i, got_v = grp.argmax_result(off_best)
+    out["argmax_matches_gathered_logits"] = bool(got_i == want and got_v == float(logits.max()))
+    out["us"], out["gbs"], out["frac_of_hbm_peak"] = (out["gather_logits"][k] for k in ("us", "gbs", "frac_of_hbm_peak"))
+    out["how"] = ("CUDA graph of dependent launches over a pool of distinct shards (> L2 per rank); "
+                  "gather_logits ends with the whole logits vector on every rank, exchange_argmax with "
+                  "the winning (value, index) pair on every rank")
+    return out
 
 
 def config4_prefill(torch, miori_b200, synth, dev, G, peaks, timed, rank, world):
@@ -638,6 +753,58 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
     ex["config1_gemv8_m1_n131072_k2048"] = {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
                                             "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     del q, s, b
+    # long stream of 4-bit weights: M=1 over two distinct 151 MB matrices (N=131072, K=2048) -- the
+    # kernel's rate once the fixed cost of a launch is amortised
+    N, K = 131072, 2048
+    big = [synth.make_weight(N, K, 4, G, seed=300 + i, device=dev) for i in range(2)]
+    y = torch.empty((1, N), device=dev)
+
+    def run_stream():
+        for q, s, b in big:
+            miori_b200.gemv4(q, s, b, x, group=G, flags=flags, out=y)
+    run_stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run_stream()
+    ms = timed(g.replay, 10) / 10 / len(big)
+    by = packed_bytes(N, K, 4, G)
+    ex["stream_gemv4_m1_n131072_k2048"] = {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
+                                           "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                           "kernel": "gemv_umma_kernel<4,1> (tcgen05.mma.kind::i8), two CTAs per SM"}
+    del big
+    # RMSNorm in front of a projection: norm kernel + GEMV against the GEMV with the norm fused into
+    # its activation staging, M=1, one layer's four shapes over pools of distinct weights (> L2)
+    fused = {}
+    for N, K in SHAPES:
+        npool = max(2, min(24, (300 << 20) // packed_bytes(N, K, 4, G)))
+        pool = [synth.make_weight(N, K, 4, G, seed=700 + i, device=dev) for i in range(npool)]
+        xf = torch.randn((1, K), device=dev)
+        gam = torch.ones(K, dtype=torch.bfloat16, device=dev)
+        xn = torch.empty((1, K), dtype=torch.bfloat16, device=dev)
+        y = torch.empty((1, N), device=dev)
+
+        def two_kernels():
+            for q, s, b in pool:
+                miori_b200.rmsnorm(xf, gam, 1e-5, flags=flags, out=xn)
+                miori_b200.gemv4(q, s, b, xn, group=G, flags=flags, out=y)
+
+        def one_kernel():
+            for q, s, b in pool:
+                miori_b200.gemv4_rmsnorm(q, s, b, xf, gam, 1e-5, group=G, flags=flags, out=y)
+        res = {}
+        for name, fn in (("norm_then_gemv_us", two_kernels), ("fused_us", one_kernel)):
+            fn()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            res[name] = 1e3 * timed(g.replay, 10) / 10 / npool
+        fused[f"N{N}_K{K}"] = res
+        del pool
+    ex["rmsnorm_fusion_m1"] = {"per_projection": fused,
+                               "layer_norm_then_gemv_us": sum(v["norm_then_gemv_us"] for v in fused.values()),
+                               "layer_fused_us": sum(v["fused_us"] for v in fused.values()),
+                               "how": "CUDA graphs of PDL launches; the unfused pair is the default GEMV after "
+                                      "miori_rmsnorm, the fused one miori_gemv4_rmsnorm (tcgen05 kernel)"}
     # config 3: prefill GEMM M=1024 on the bf16 cache + cache build.  Each shape runs over a
     # pool of distinct caches larger than L2 (weights come from HBM, as in a real prefill where
     # consecutive layers evict each other), one CUDA graph of PDL launches per shape.

@@ -67,6 +67,16 @@ void dequant8(Metal& m, MTL::ComputeCommandEncoder* e, const Weights& w, const T
 void gemm_naive(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
                 MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t lda, uint32_t ldb,
                 uint32_t ldc, uint32_t aoff = 0, uint32_t boff = 0, uint32_t coff = 0);
+// reference src/ops.h:16-18 -- y (bf16) = x (f32) * rsqrt(mean(x^2) + eps) * gamma, row by row
+void rmsnorm(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* x, const Weights& w,
+             const Tensor& gamma, MTL::Buffer* y, uint32_t rows, uint32_t n, float eps);
+// reference src/ops.h:23-24 -- out (bf16) = silu(gate) * up, both f32
+void silu_mul(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* gate, MTL::Buffer* up,
+              MTL::Buffer* out, uint32_t n);
+// reference src/ops.h:35-37 -- rows tokens[t] of the 8-bit table as bf16 [T][K]
+void embed8(Metal& m, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q,
+            const Tensor& s, const Tensor& b, MTL::Buffer* tokens, MTL::Buffer* out, uint32_t T,
+            uint32_t K);
 // reference src/ops.h:207-209 -- the small-M tile shape; same kernel, same result per row
 void gemm_mpp32(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
                 MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t boff = 0);

@@ -221,6 +221,24 @@ void gemm_naive(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buff
           "gemm_naive");
 }
 
+void rmsnorm(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* x, const Weights& w, const Tensor& gamma,
+             MTL::Buffer* y, uint32_t rows, uint32_t n, float eps) {
+    check(miori_rmsnorm(at(x, 0), at(w.buffer(), gamma.begin), at_mut(y, 0), rows, n, eps, 0, e->stream()),
+          "rmsnorm");
+}
+
+void silu_mul(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* gate, MTL::Buffer* up, MTL::Buffer* out,
+              uint32_t n) {
+    check(miori_silu_mul(at(gate, 0), at(up, 0), at_mut(out, 0), n, 0, e->stream()), "silu_mul");
+}
+
+void embed8(Metal&, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q, const Tensor& s,
+            const Tensor& b, MTL::Buffer* tokens, MTL::Buffer* out, uint32_t T, uint32_t K) {
+    check(miori_embed8(at(w.buffer(), q.begin), at(w.buffer(), s.begin), at(w.buffer(), b.begin),
+                       at(tokens, 0), at_mut(out, 0), T, (uint32_t)q.rows(), K, kGroup, 0, e->stream()),
+          "embed8");
+}
+
 void gemm_mpp32(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
                 MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t boff) {
     gemm_mpp_off(m, e, A, B, C, M, N, K, 0, boff, 0);
