@@ -44,53 +44,56 @@ def packed_bytes(N, K, bits, group):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons sampled (NVML, every 50 ms) while the measurements run."""
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.samples, self.reasons, self.stop_flag, self.t = index, [], set(), False, None
+        self.max_mhz, self.err = None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._pump, daemon=True)
-            self.t.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # no NVML: report that instead of clocks
+            self.err = f"NVML unavailable: {e}"
+            return
+        self.t = threading.Thread(target=self._pump, daemon=True)
+        self.t.start()
 
     def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+        nv = self.nv
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        while not self.stop_flag:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for nm, bit in names.items():
+                    if bits & bit:
+                        self.reasons.add(nm)
+            except Exception as e:
+                self.err = str(e)
+                return
+            time.sleep(0.05)
+
+    def clear(self):
+        self.samples, self.reasons = [], set()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for nm, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(nm)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        self.stop_flag = True
+        if self.t is not None:
+            self.t.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0,
+                    "reasons": [self.err or "no samples"]}
+        sm = sorted(self.samples)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_mhz, "samples": len(sm),
+                "reasons": sorted(self.reasons)}
 
 
 def measured_peaks():
@@ -202,6 +205,61 @@ def run_reference_arm(args):
 METRIC = "int4 GEMV effective HBM GB/s (M=1-32)"
 
 
+def run_one(a):
+    """`--one`: a single operator on synthetic data, `--reps` timed launches per weight tensor after
+    one untimed pass; prints the CUDA-event time per launch.  The weights come from a pool of
+    `--pool` distinct tensors so that a working set larger than L2 can be asked for."""
+    import torch
+    import miori_b200
+    from miori_b200 import synth
+
+    dev = "cuda:0"
+    G = a.group
+    bits = a.bits if a.one.startswith("gemv") else 4
+    pool = [synth.make_weight(a.n, a.k, bits, G, seed=i, device=dev) for i in range(a.pool)]
+    x = synth.make_activation(a.m, a.k, seed=99, device=dev)
+    wbytes = packed_bytes(a.n, a.k, bits, G)
+
+    def time_ms(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / a.reps / a.pool
+
+    if a.one == "gemv":
+        fn = miori_b200.gemv4 if bits == 4 else miori_b200.gemv8
+        y = torch.empty((a.m, a.n), device=dev)
+        ms = time_ms(lambda: [fn(q, s, b, x, group=G, flags=a.flags, out=y) for q, s, b in pool])
+        print(f"gemv{bits} N={a.n} K={a.k} M={a.m} g={G} flags={a.flags:#x}: {ms * 1e3:.2f} us/launch "
+              f"{wbytes / ms / 1e6:.0f} GB/s")
+    elif a.one == "gemv_rmsnorm":
+        fn = miori_b200.gemv4_rmsnorm if bits == 4 else miori_b200.gemv8_rmsnorm
+        xf = x.float()
+        gamma = synth.make_activation(1, a.k, seed=98, device=dev).float().reshape(-1)
+        y = torch.empty((a.m, a.n), device=dev)
+        ms = time_ms(lambda: [fn(q, s, b, xf, gamma, 1e-5, group=G, flags=a.flags, out=y) for q, s, b in pool])
+        print(f"gemv{bits}_rmsnorm N={a.n} K={a.k} M={a.m} g={G}: {ms * 1e3:.2f} us/launch "
+              f"{wbytes / ms / 1e6:.0f} GB/s")
+    elif a.one == "dequant":
+        out = torch.empty((a.n, a.k), dtype=torch.bfloat16, device=dev)
+        ms = time_ms(lambda: [miori_b200.dequant4_rowmajor(q, s, b, group=G, out=out) for q, s, b in pool])
+        print(f"dequant4 N={a.n} K={a.k}: {ms * 1e3:.2f} us/launch {(wbytes + 2 * a.n * a.k) / ms / 1e6:.0f} GB/s")
+    else:
+        caches = [miori_b200.dequant4_cache(q, s, b, group=G) for q, s, b in pool]
+        del pool
+        ws = miori_b200.gemm_workspace(a.m, a.n, a.k, dev)
+        Cm = torch.empty((a.m, a.n), device=dev)
+        ms = time_ms(lambda: [miori_b200.gemm_bf16_cache(x, c, a.n, flags=a.flags, out=Cm, workspace=ws)
+                              for c in caches])
+        print(f"gemm M={a.m} N={a.n} K={a.k}: {ms * 1e3:.2f} us/launch "
+              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.0f} TFLOP/s")
+
+
 def workload_config(args):
     """The workload both arms print (identical dicts: the driver compares them)."""
     return {"workload": "decode_stack_int4: 24 layers x {2048->3072, 2048->2048, 2048->16384, "
@@ -235,9 +293,21 @@ def main():
                          "profiler's launch list; timings then include host launch overhead)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="stack depth (24 is the benchmark)")
     ap.add_argument("--verbose", action="store_true", help="progress on stderr")
+    one = ap.add_argument_group("one operator on one GPU (--one): a small case to time or to profile")
+    one.add_argument("--one", choices=["gemv", "gemv_rmsnorm", "gemm", "dequant"])
+    one.add_argument("--bits", type=int, default=4, choices=[4, 8])
+    one.add_argument("--n", type=int, default=8192)
+    one.add_argument("--k", type=int, default=2048)
+    one.add_argument("--m", type=int, default=1)
+    one.add_argument("--pool", type=int, default=1, help="distinct weight tensors visited in turn")
+    one.add_argument("--reps", type=int, default=5)
+    one.add_argument("--flags", type=lambda v: int(v, 0), default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.one:
+        run_one(args)
         return
 
     import torch
@@ -265,12 +335,9 @@ def main():
     pdl = 0 if args.no_pdl else miori_b200.LAUNCH_PDL
 
     # ---- which projections are split by rows over the ranks
-    def is_sharded(i):
-        N, K = SHAPES[i]
-        if world == 1 or args.shard == "none":
-            return False
-        return args.shard == "all" or packed_bytes(N, K, 4, G) >= args.shard_bytes
-    sharded = [is_sharded(i) for i in range(len(SHAPES))]
+    from miori_b200 import shard as shard_plan
+    sharded = shard_plan.split_plan([packed_bytes(N, K, 4, G) for N, K in SHAPES], world, args.shard_bytes,
+                                    args.shard)
 
     def shard_rows(t, N):
         rows = N // world
@@ -491,7 +558,7 @@ def main():
     for _ in range(max(3, args.warmup)):
         step()
     if rank == 0:
-        sampler.lines.clear()  # keep only samples taken under load: the timed region and all that follows
+        sampler.clear()  # keep only samples taken under load: the timed region and all that follows
     ms_total = timed(step, args.steps)
     ms_step = ms_total / args.steps
     say(f"timed region done: {ms_step:.3f} ms/step")
@@ -561,9 +628,9 @@ def main():
 
     peaks, peak_kind = measured_peaks()
     m1 = per_m["1"]
-    # DRAM bytes (read + write) per algorithmic byte of gemv_tma_kernel, from the ncu capture
-    # summarised in profiles/gemv_tma_n131072_k2048_m1.md (156.1 MB moved for 151.0 MB of
-    # weights); traffic grows in proportion to the weights a launch streams
+    # DRAM bytes (read + write) per algorithmic byte of gemv_tma_kernel, from an ncu capture of
+    # the N=131072, K=2048, M=1 case (156.1 MB moved for 151.0 MB of weights); traffic grows in
+    # proportion to the weights a launch streams
     DRAM_PER_ALGO_BYTE = 1.034
     roofline = {
         "kernel": "gemv_tma_kernel<4,exact,1> (M=1 pass of the stack, 96 launches per pass)",
@@ -686,7 +753,7 @@ def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world,
 
 
 def config4_prefill(torch, miori_b200, synth, dev, G, peaks, timed, rank, world):
-    """BASELINE config 4: 64 prompts x 2048 tokens = 131072 rows through the four projection
+    """Prefill configuration: 64 prompts x 2048 tokens = 131072 rows through the four projection
     shapes, token rows split evenly over the ranks, bf16 cache replicated, no collective.
     `timed` brackets with barriers and takes the max over ranks; TFLOP/s is the whole job's."""
     M_total = 131072

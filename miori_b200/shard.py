@@ -62,3 +62,43 @@ def gather_rows(y_local: torch.Tensor, N: int, group=None) -> torch.Tensor:
 def token_range(M: int, rank: int, world: int) -> tuple[int, int]:
     """Rows of A (tokens) this rank multiplies in the M-sharded prefill GEMM."""
     return row_range(M, rank, world, 1)
+
+
+def split_plan(weight_bytes: list[int], world: int, threshold_bytes: int, mode: str = "policy") -> list[bool]:
+    """Which projections of a decode chain are split by output rows.  A split saves
+    weight_bytes * (1 - 1/world) of streaming per launch and costs one exchange of y, so it pays
+    only above a size; below it every rank computes the whole projection and nothing crosses
+    NVLink.  mode: "policy" (by `threshold_bytes`), "all", "none"."""
+    if mode not in ("policy", "all", "none"):
+        raise ValueError(f"unknown sharding mode {mode!r}")
+    if world <= 1 or mode == "none":
+        return [False] * len(weight_bytes)
+    return [mode == "all" or nbytes >= threshold_bytes for nbytes in weight_bytes]
+
+
+def better(a: tuple[float, int], b: tuple[float, int]) -> bool:
+    """Order of the arg-max candidates (value, index): larger value first, then the lower index,
+    so the winner is the first maximum of the unsharded vector; NaN never wins."""
+    if a[0] != a[0]:
+        return False
+    return b[0] != b[0] or a[0] > b[0] or (a[0] == b[0] and a[1] < b[1])
+
+
+def argmax_exchange(v_local: torch.Tensor, index0: int, group=None) -> tuple[int, float]:
+    """Greedy pick over a vector split across ranks: every rank offers its best (value, index),
+    the pairs are exchanged (2 words per rank instead of the whole vector) and every rank picks
+    the same winner.  Host-side statement of what miori_argmax_allreduce does over peer stores."""
+    v = v_local.reshape(-1).float()
+    i = int(torch.argmax(torch.nan_to_num(v, nan=float("-inf"))).item()) if v.numel() else 0
+    mine = torch.tensor([float(v[i]) if v.numel() else float("nan"), float(index0 + i)], dtype=torch.float64,
+                        device=v.device)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return int(mine[1].item()), float(mine[0].item())
+    pairs = torch.empty(world * 2, dtype=torch.float64, device=v.device)
+    dist.all_gather_into_tensor(pairs, mine, group=group)
+    best = (float("nan"), -1)
+    for val, idx in pairs.view(world, 2).cpu().tolist():
+        if better((val, int(idx)), best):
+            best = (val, int(idx))
+    return best[1], best[0]

@@ -1,18 +1,27 @@
-"""Self-check of the multi-GPU path: run one process per GPU, e.g.
+"""Self-check of the multi-GPU path (a test helper, not part of the package): run one process per
+GPU from the repository root, e.g.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29533 -m miori_b200.peers_check
+        --master-port 29533 tests/peers_check.py
 
 Every rank holds a row shard of the same seeded weights, runs the N-sharded GEMV whose epilogue
 stores into all ranks' arenas, and compares its gathered y bit for bit with the single-GPU GEMV
 over the whole matrix: eagerly, back to back with programmatic dependent launch, inside a replayed
-CUDA graph, for 8-bit weights with bf16 output, and for the stand-alone all-gather.  Exits non-zero
-on any mismatch or if a bounded wait expired.
+CUDA graph, for 8-bit weights with bf16 output, for the stand-alone all-gather and for the
+exchange of (value, index) pairs that finishes a sharded arg-max.  Exits non-zero on any mismatch
+or if a bounded wait expired.
+
+The last part checks the failure path without faulting anything: in a second group whose wait
+limit is 20 ms, rank 1 leaves one launch out; every other rank's kernel gives up waiting for
+rank 1's rows, returns, and the host reads the error (a device status, then MioriError from
+`status()`).  Nobody exits before a host barrier, so no arena is unmapped under a store.
 """
 from __future__ import annotations
 
 import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 import torch.distributed as dist
@@ -35,6 +44,11 @@ def main() -> int:
     grp = PeerGroup(rank, world, 16 << 20, dev)
     failures = []
 
+    def host_barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
     def expect(ok, what):
         if not ok:
             failures.append(what)
@@ -42,6 +56,9 @@ def main() -> int:
     q, s, b = synth.make_weight(N, K, 4, G, seed=11, device=dev)
     qs, ss, bs = q[r0:r0 + rows].contiguous(), s[r0:r0 + rows].contiguous(), b[r0:r0 + rows].contiguous()
     pdl = miori_b200.LAUNCH_PDL
+    # the kernels' waits for a peer are bounded (about a second): start level, whatever the ranks'
+    # set-up cost was
+    host_barrier()
 
     # eager, several launches in a row into the same y (exercises the ready/done counters)
     for M in (1, 2, 4, 8, 16):
@@ -95,17 +112,63 @@ def main() -> int:
         torch.cuda.synchronize()
         expect(torch.equal(grp.tensor(offa, (M, N)), full + it), f"allgather {it}")
 
+    # sharded arg-max: every rank offers its best (value, index), all end with the same winner;
+    # ties go to the lowest index
+    for dt in (torch.float32, torch.bfloat16):
+        for it in range(3):
+            gen = torch.Generator(device="cpu").manual_seed(500 + it)
+            v = torch.randn(N, generator=gen).to(dt)
+            if it == 2:  # the same maximum on every rank
+                v[torch.arange(world) * rows + 7] = 9.0
+            offb = grp.alloc((2 * world + 2) * 4)
+            grp.argmax_allreduce(v[r0:r0 + rows].to(dev).contiguous(), r0, offb, flags=pdl)
+            torch.cuda.synchronize()
+            want_v = float(v.float().max())
+            want_i = int(torch.nonzero(v.float() == want_v)[0, 0])
+            expect(grp.argmax_result(offb) == (want_i, want_v), f"argmax exchange {dt} case {it}")
+
     try:
         grp.status()
     except Exception as e:  # a bounded wait expired on this rank
         failures.append(str(e))
     expect(miori_b200.lib.miori_device_error_poll() == 0, "device error recorded")
+    host_barrier()  # nobody unmaps an arena while a peer may still store into it
+    grp.close()
+
+    # the failure path: a peer that never sends.  Rank 1 skips one launch; the others' waits expire.
+    if world > 1:
+        grp = PeerGroup(rank, world, 1 << 20, dev)
+        grp.set_wait_us(20000)
+        offe = grp.alloc(N * 4)
+        xe = synth.make_activation(1, K, seed=5, device=dev)
+        host_barrier()
+        grp.gemv_allgather(4, qs, ss, bs, xe, offe, r0, N, group=G)  # a complete launch first
+        host_barrier()
+        expect(torch.equal(grp.tensor(offe, (1, N)), miori_b200.gemv4(q, s, b, xe, group=G)), "launch before the gap")
+        if rank != 1:
+            grp.gemv_allgather(4, qs, ss, bs, xe, offe, r0, N, group=G)
+        torch.cuda.synchronize()  # returns: the wait is bounded
+        raised = False
+        try:
+            grp.status()
+        except miori_b200.MioriError as e:
+            raised = "gave up waiting" in str(e)
+        code = miori_b200.lib.miori_device_error_poll()
+        if rank != 1:
+            expect(raised, "status() did not report the expired wait")
+            expect(code != 0, "no device error recorded for the expired wait")
+        else:
+            expect(not raised and code == 0, "the rank that skipped its launch reports an error")
+        # the context is still usable after the expiry
+        y_after = miori_b200.gemv4(q, s, b, xe, group=G)
+        torch.cuda.synchronize()
+        expect(bool(torch.isfinite(y_after).all()), "launch after the expired wait")
     bad = torch.tensor([len(failures)])
     if world > 1:
         dist.all_reduce(bad)
-        dist.barrier()  # nobody unmaps an arena while a peer may still store into it
-    torch.cuda.synchronize()
-    grp.close()
+    host_barrier()
+    if world > 1:
+        grp.close()
     if failures:
         print(f"[peers_check rank {rank}] FAILED: {failures}", file=sys.stderr, flush=True)
     if rank == 0:

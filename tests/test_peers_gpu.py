@@ -59,7 +59,7 @@ def test_two_ranks_gather_bit_exact():
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-         "--master-addr", "127.0.0.1", "--master-port", "29533", "-m", "miori_b200.peers_check"],
+         "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(ROOT, "tests", "peers_check.py")],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "peers_check: ok" in r.stdout

@@ -69,3 +69,51 @@ def test_sharded_gemv_allgather_world2(tmp_path, N):
     y, want = np.load(out + ".y.npy"), np.load(out + ".want.npy")
     assert y.shape == want.shape and np.array_equal(y, want)
     assert np.array_equal(np.load(out + ".c0.npy"), np.load(out + ".cfull.npy"))
+
+
+def test_split_plan():
+    sizes = [3 << 20, 2 << 20, 18 << 20, 9 << 20]
+    assert shard.split_plan(sizes, 1, 16 << 20) == [False] * 4
+    assert shard.split_plan(sizes, 8, 16 << 20) == [False, False, True, False]
+    assert shard.split_plan(sizes, 2, 16 << 20, "all") == [True] * 4
+    assert shard.split_plan(sizes, 2, 16 << 20, "none") == [False] * 4
+    with pytest.raises(ValueError):
+        shard.split_plan(sizes, 2, 1, "some")
+
+
+def test_argmax_candidate_order():
+    nan = float("nan")
+    assert shard.better((2.0, 9), (1.0, 0))
+    assert shard.better((1.0, 3), (1.0, 4)) and not shard.better((1.0, 4), (1.0, 3))
+    assert not shard.better((nan, 0), (-1e30, 5)) and shard.better((-1e30, 5), (nan, 0))
+
+
+def _argmax_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    got = []
+    for case in range(4):
+        v = torch.randn(1000, generator=torch.Generator().manual_seed(case))
+        if case == 1:    # the same maximum on both ranks: the lower index wins
+            v[[17, 600]] = 7.0
+        if case == 2:    # the maximum is the very last element
+            v[999] = 8.0
+        if case == 3:    # one rank holds nothing but NaN
+            v[:500] = float("nan")
+        r0, r1 = shard.row_range(1000, rank, world, 1)
+        idx, val = shard.argmax_exchange(v[r0:r1], r0)
+        want = int(torch.argmax(torch.nan_to_num(v, nan=float("-inf"))))
+        got.append((idx, val, want, float(v[want])))
+    np.save(out + f".{rank}.npy", np.array(got, dtype=np.float64))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_argmax_exchange_world2(tmp_path):
+    out = str(tmp_path / "a")
+    mp.spawn(_argmax_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    r0, r1 = np.load(out + ".0.npy"), np.load(out + ".1.npy")
+    assert np.array_equal(r0, r1)                      # every rank ends with the same winner
+    assert np.array_equal(r0[:, 0], r0[:, 2]) and np.array_equal(r0[:, 1], r0[:, 3])
+    assert r0[1, 0] == 17 and r0[2, 0] == 999 and r0[3, 0] >= 500
