@@ -17,7 +17,8 @@ every M of the sweep.
 With torchrun (N>1) the total work is fixed (strong scaling).  A projection is split by output
 rows over the ranks, its y gathered by peer stores from the GEMV's own epilogue (or by
 ncclAllGather with --allgather nccl), only when its weights are large enough for the split to
-pay (--shard policy, the default); the others are computed by every rank.  Outside the timed
+pay; the others are computed by every rank.  By default (--shard auto) both choices are replayed
+for every M before the timed region and the faster one is kept.  Outside the timed
 region every rank checks one forced-sharded pass against the single-GPU kernels.
 """
 from __future__ import annotations
@@ -44,7 +45,7 @@ def packed_bytes(N, K, bits, group):
 
 
 class ClockSampler:
-    """SM clock and throttle reasons sampled (NVML, every 50 ms) while the measurements run."""
+    """SM clock and throttle reasons sampled (NVML, every few milliseconds) while the measurements run."""
 
     def __init__(self, index):
         self.index, self.samples, self.reasons, self.stop_flag, self.t = index, [], set(), False, None
@@ -79,7 +80,7 @@ class ClockSampler:
             except Exception as e:
                 self.err = str(e)
                 return
-            time.sleep(0.05)
+            time.sleep(0.004)
 
     def clear(self):
         self.samples, self.reasons = [], set()
@@ -283,9 +284,10 @@ def main():
     ap.add_argument("--allgather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: gather y by peer stores from the GEMV epilogue (default) or with "
                          "ncclAllGather after each launch")
-    ap.add_argument("--shard", default="policy", choices=["policy", "all", "none"],
+    ap.add_argument("--shard", default="auto", choices=["auto", "policy", "all", "none"],
                     help="N > 1: which projections are split by rows over the ranks: those whose packed "
-                         "weights reach --shard-bytes (policy), all of them, or none")
+                         "weights reach --shard-bytes (policy), all of them, none, or per batch size "
+                         "whichever of policy / none replays faster (auto)")
     ap.add_argument("--shard-bytes", type=int, default=16 << 20,
                     help="policy: a projection is split when its packed weights reach this many bytes")
     ap.add_argument("--eager", action="store_true",
@@ -334,28 +336,29 @@ def main():
     G = args.group
     pdl = 0 if args.no_pdl else miori_b200.LAUNCH_PDL
 
-    # ---- which projections are split by rows over the ranks
+    # ---- which projections are split by rows over the ranks.  Every rank holds the whole stack
+    # (0.7 GB); a split projection reads only its own rows of q / s / b (rows are contiguous, so a
+    # shard is a view), which lets the split be decided per projection and per batch size.
     from miori_b200 import shard as shard_plan
-    sharded = shard_plan.split_plan([packed_bytes(N, K, 4, G) for N, K in SHAPES], world, args.shard_bytes,
-                                    args.shard)
+    wbytes = [packed_bytes(N, K, 4, G) for N, K in SHAPES]
+    no_split = [False] * len(SHAPES)
+    if args.shard == "auto":
+        candidates = [no_split, shard_plan.split_plan(wbytes, world, args.shard_bytes, "policy")]
+    else:
+        candidates = [shard_plan.split_plan(wbytes, world, args.shard_bytes, args.shard)]
+    candidates = [c for n, c in enumerate(candidates) if c not in candidates[:n]]
+    split = {M: candidates[-1] for M in M_SWEEP}   # per M; settled by measurement below when "auto"
 
-    def shard_rows(t, N):
+    def my_rows(t, N):
         rows = N // world
-        return t[rank * rows:(rank + 1) * rows].contiguous()
+        return t[rank * rows:(rank + 1) * rows]
 
-    # ---- weights: the row shard of a split projection, the whole matrix of the others.  The last
-    # layer is kept in both forms on every rank for the parity check below.
-    stack, last_full, last_shard = [], [], []
+    stack = []
     for l in range(layers):
         projs = []
         for i, (N, K) in enumerate(SHAPES):
             assert N % (16 * world) == 0
-            q, s, b = synth.make_weight(N, K, 4, G, seed=1234 + l * 4 + i, device=dev)
-            if l == layers - 1 and world > 1:
-                last_full.append((q, s, b))
-                last_shard.append((shard_rows(q, N), shard_rows(s, N), shard_rows(b, N)))
-            projs.append((shard_rows(q, N), shard_rows(s, N), shard_rows(b, N)) if sharded[i] else (q, s, b))
-            del q, s, b
+            projs.append(synth.make_weight(N, K, 4, G, seed=1234 + l * 4 + i, device=dev))
         stack.append(projs)
     bytes_pass = layers * sum(packed_bytes(N, K, 4, G) for N, K in SHAPES)  # whole job
     say("weights ready")
@@ -373,13 +376,14 @@ def main():
     def flat_len(shapes):
         return sum((a * b + 127) // 128 * 128 for a, b in shapes)
 
-    x_flat, x_dev, y_loc = {}, {}, {}
+    x_flat, x_dev, y_loc, y_part = {}, {}, {}, {}
     for M in M_SWEEP:
         xs = [(M, K) for _, K in SHAPES]
         x_flat[M] = torch.empty(flat_len(xs), dtype=torch.bfloat16, device=dev)
         x_dev[M] = carve(x_flat[M], xs)
-        # local outputs: this rank's rows of a split projection, all rows of the others
-        y_loc[M] = [torch.empty((M, N // world if sharded[i] else N), device=dev) for i, (N, _) in enumerate(SHAPES)]
+        # outputs of unsplit projections, and this rank's rows of a split one on the cache-GEMM path
+        y_loc[M] = [torch.empty((M, N), device=dev) for N, _ in SHAPES]
+        y_part[M] = [torch.empty((M, N // world), device=dev) for N, _ in SHAPES] if world > 1 else None
         for v, (_, K) in zip(x_dev[M], SHAPES):
             v.copy_(synth.make_activation(M, K, seed=50 + M, device=dev))
     # N > 1: the gathered outputs of split projections.  "peer": y[M][N] at the same offset of every
@@ -399,45 +403,47 @@ def main():
     def gathered(M, i):
         """Where the whole y of projection i ends up on this rank."""
         N = SHAPES[i][0]
-        if not sharded[i]:
+        if not split[M][i]:
             return y_loc[M][i]
         if grp is not None:
             return grp.tensor(y_off[M][i], (M, N))
         return y_nccl[M][i]
-    y_nccl = {M: [torch.empty((world * M, N // world), device=dev) if sharded[i] and grp is None else None
-                  for i, (N, _) in enumerate(SHAPES)] for M in M_SWEEP}
+    y_nccl = {M: [torch.empty((world * M, N // world), device=dev) if world > 1 and grp is None else None
+                  for N, _ in SHAPES] for M in M_SWEEP}
 
     # bf16 caches for the wide-batch path (M > 8 goes through the cache GEMM, the reference's
     # own policy for wide batches) and one split-K workspace shared by the in-order launches
     caches = [[miori_b200.dequant4_cache(q, s, b, group=G) for (q, s, b) in projs] for projs in stack]
-    ws_bytes = max(lib.miori_gemm_workspace_bytes(M, N // world if sharded[i] else N, K)
-                   for M in M_SWEEP for i, (N, K) in enumerate(SHAPES))
+    ws_bytes = max(lib.miori_gemm_workspace_bytes(M, rows, K)
+                   for M in M_SWEEP for N, K in SHAPES for rows in (N, N // world))
     ws = torch.empty(max(ws_bytes // 4, 4), dtype=torch.float32, device=dev)
 
     def packed_path(M, K):  # miori_linear4's own rule
         return M <= 8 or (M <= 16 and K <= 2048)
 
-    def run_proj(M, i, w, cache, x, split):
+    def run_proj(M, i, w, cache, x, do_split):
         """One projection: on this rank's rows with the result gathered everywhere (split), or whole."""
         N, K = SHAPES[i]
         q, s, b = w
-        if not split:
+        if not do_split:
             miori_b200.linear4(q, s, b, cache, x, group=G, flags=pdl, out=y_loc[M][i], workspace=ws)
             return
+        q, s, b, cache = my_rows(q, N), my_rows(s, N), my_rows(b, N), my_rows(cache, N)
         if grp is not None and packed_path(M, K):
             grp.gemv_allgather(4, q, s, b, x, y_off[M][i], rank * (N // world), N, group=G, flags=pdl)
             return
-        y = y_loc[M][i] if sharded[i] else torch.empty((M, N // world), device=dev)
+        y = y_part[M][i]
         miori_b200.linear4(q, s, b, cache, x, group=G, flags=pdl, out=y, workspace=ws)
         if grp is not None:
             grp.allgather(y, y_off[M][i], rank * (N // world), N, flags=pdl)
         else:
             dist.all_gather_into_tensor(y_nccl[M][i], y)
 
-    def one_pass(M):
+    def one_pass(M, plan=None):
+        plan = split[M] if plan is None else plan
         for projs, cs in zip(stack, caches):
             for i, (w, c, x) in enumerate(zip(projs, cs, x_dev[M])):
-                run_proj(M, i, w, c, x, sharded[i])
+                run_proj(M, i, w, c, x, plan[i])
 
     # ---- parity of the split path (N > 1, outside every timed region): the last layer's four
     # projections, forced through the row split at M = 1 and M = 32, against the same kernels on
@@ -445,16 +451,15 @@ def main():
     # K split by shape, so its rows agree to fp32 rounding.
     parity = None
     if world > 1:
-        keep = (sharded, y_off)
         cases, worst_gemm, bad = 0, 0.0, []
         for M in (1, 32):
             tmp_off = [grp.alloc(M * N * 4) if grp is not None else None for N, _ in SHAPES]
             for i, (N, K) in enumerate(SHAPES):
-                full, part = last_full[i], last_shard[i]
+                full = stack[-1][i]
+                part = tuple(my_rows(t, N) for t in full)
                 x = x_dev[M][i]
-                want = miori_b200.linear4(*full, miori_b200.dequant4_cache(*full, group=G), x, group=G,
-                                          workspace=ws)
-                c_part = miori_b200.dequant4_cache(*part, group=G)
+                want = miori_b200.linear4(*full, caches[-1][i], x, group=G, workspace=ws)
+                c_part = my_rows(caches[-1][i], N)
                 rows = N // world
                 if grp is not None and packed_path(M, K):
                     grp.gemv_allgather(4, *part, x, tmp_off[i], rank * rows, N, group=G, flags=pdl)
@@ -487,52 +492,7 @@ def main():
         if int(flag.item()) != 0:
             print(f"[bench rank {rank}] sharded path differs from the single-GPU kernels: {bad}",
                   file=sys.stderr, flush=True)
-        del last_full, last_shard
         say(f"parity: {parity}")
-
-    # ---- capture one CUDA graph per M
-    for M in M_SWEEP:
-        one_pass(M)
-    torch.cuda.synchronize()
-    say("eager passes done")
-    class Eager:
-        def __init__(self, M):
-            self.M = M
-
-        def replay(self):
-            one_pass(self.M)
-
-    graphs = {}
-    for M in M_SWEEP:
-        if args.eager:
-            graphs[M] = Eager(M)
-            continue
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            one_pass(M)
-        graphs[M] = g
-    launches_pass = layers * len(SHAPES)
-    if world > 1:
-        # every rank has instantiated its graphs before anyone replays: the kernels' waits for a peer
-        # are bounded, and a rank still capturing would look like a missing one
-        torch.cuda.synchronize()
-        dist.barrier()
-
-    def kernels_in_pass(M):  # this library's kernel launches in one pass at M rows, on one rank
-        n = 0
-        for i, (N, K) in enumerate(SHAPES):
-            if packed_path(M, K):
-                n += 1
-                continue
-            rows = N // world if sharded[i] else N
-            n += 2 if lib.miori_gemm_workspace_bytes(M, rows, K) else 1   # GEMM (+ K-split sum)
-            n += 1 if (grp is not None and sharded[i]) else 0             # peer all-gather
-        return layers * n
-    say("graphs captured")
-
-    def step():
-        for M in M_SWEEP:
-            graphs[M].replay()
 
     def barrier():
         if world > 1:
@@ -551,6 +511,64 @@ def main():
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
+
+    # ---- one CUDA graph per M.  With --shard auto (N > 1) every candidate split is captured and
+    # replayed a few times, and the faster one is kept: the time is the maximum over the ranks, so
+    # all ranks keep the same one.  Replicating a projection costs HBM time, splitting it costs an
+    # exchange over NVLink; which is cheaper depends on the rows a rank keeps and on M.
+    class Eager:
+        def __init__(self, M, plan):
+            self.M, self.plan = M, plan
+
+        def replay(self):
+            one_pass(self.M, self.plan)
+
+    def capture(M, plan):
+        one_pass(M, plan)
+        torch.cuda.synchronize()
+        if args.eager:
+            return Eager(M, plan)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            one_pass(M, plan)
+        return g
+
+    graphs, tuning = {}, {}
+    for M in M_SWEEP:
+        best = None
+        for plan in candidates:
+            g = capture(M, plan)
+            if len(candidates) == 1:
+                best = (0.0, plan, g)
+                break
+            # every rank has instantiated this graph before anyone replays it: the kernels' waits for
+            # a peer are bounded, and a rank still capturing would look like a missing one
+            barrier()
+            timed(g.replay, 3)
+            ms = timed(g.replay, 10) / 10
+            tuning.setdefault(str(M), {})["+".join(f"{K}->{N}" for (N, K), sp in zip(SHAPES, plan) if sp)
+                                           or "none"] = ms * 1e3
+            if best is None or ms < best[0]:
+                best = (ms, plan, g)
+        graphs[M], split[M] = best[2], best[1]
+    launches_pass = layers * len(SHAPES)
+    barrier()
+
+    def kernels_in_pass(M):  # this library's kernel launches in one pass at M rows, on one rank
+        n = 0
+        for i, (N, K) in enumerate(SHAPES):
+            if packed_path(M, K):
+                n += 1
+                continue
+            rows = N // world if split[M][i] else N
+            n += 2 if lib.miori_gemm_workspace_bytes(M, rows, K) else 1   # GEMM (+ K-split sum)
+            n += 1 if (grp is not None and split[M][i]) else 0            # peer all-gather
+        return layers * n
+    say("graphs captured")
+
+    def step():
+        for M in M_SWEEP:
+            graphs[M].replay()
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -650,8 +668,10 @@ def main():
         "gpu_launches": args.steps * sum(kernels_in_pass(M) for M in M_SWEEP),
         "per_m": per_m, "roofline": roofline,
         "sharding": {"mode": args.shard if world > 1 else "single GPU", "threshold_bytes": args.shard_bytes,
-                     "split": [f"{K}->{N}" for (N, K), sp in zip(SHAPES, sharded) if sp],
-                     "replicated": [f"{K}->{N}" for (N, K), sp in zip(SHAPES, sharded) if not sp]},
+                     "weights": "replicated; a split projection reads only its own rows",
+                     "split_per_m": {str(M): [f"{K}->{N}" for (N, K), sp in zip(SHAPES, split[M]) if sp]
+                                     for M in M_SWEEP},
+                     "candidates_us_per_pass": tuning},
     }
     if parity is not None:
         out["parity"] = parity

@@ -154,14 +154,63 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
     }
 }
 
-// The same staging in one pass, for rows short enough that every thread handles one or two
+// The same staging in one pass: a thread loads a unit, stores it permuted, and the 4 (PAIR: 8)
+// lanes that hold a chunk (a 64-weight group) add up its fp32 sum with shuffles, so x is read once
+// and there is one load latency instead of two.  Two units per thread and trip, both loads issued
+// before either is used, so that a long row (K = 8192: four units per thread) costs two load
+// latencies, not four.  Whole warps iterate (THREADS and the units per row are multiples of 32
+// resp. 16, so lane groups never straddle a chunk).
+template <int BITS, bool EXACT, int MP, bool PAIR>
+__device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, uint4* xs,
+                                                float* xsum, uint32_t M, uint32_t K,
+                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
+    static_assert(BITS == 4, "one-pass staging exists for 4-bit codes only (8-bit x is staged as scaled fp16)");
+    static_assert(MP <= 4, "row index by comparison");
+    constexpr int KU = 8;
+    const uint32_t upr = steps_p * 16u;  // logical units per row
+    const uint32_t total = (uint32_t)MP * upr, lane = threadIdx.x & 31u;
+    for (uint32_t i0 = threadIdx.x - lane; i0 < total; i0 += 2u * THREADS) {
+        uint32_t i[2], m[2], u[2];
+        bool live[2];
+        uint4 v[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            i[h] = i0 + lane + (uint32_t)h * THREADS;
+            m[h] = (i[h] >= upr ? 1u : 0u) + (MP > 2 ? (i[h] >= 2u * upr ? 1u : 0u) + (i[h] >= 3u * upr ? 1u : 0u) : 0u);
+            u[h] = i[h] - m[h] * upr;
+            live[h] = i[h] < total && m[h] < M && u[h] * KU < K;
+            v[h] = make_uint4(0u, 0u, 0u, 0u);
+            if (live[h]) v[h] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m[h] * K) + u[h]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (i0 + (uint32_t)h * THREADS >= total) break;  // warp-uniform
+            uint4 o;
+            o.x = __byte_perm(v[h].x, v[h].z, 0x5410);  // (x0,x4)
+            o.y = __byte_perm(v[h].x, v[h].z, 0x7632);  // (x1,x5)
+            o.z = __byte_perm(v[h].y, v[h].w, 0x5410);  // (x2,x6)
+            o.w = __byte_perm(v[h].y, v[h].w, 0x7632);  // (x3,x7)
+            if (i[h] < total) xs[(size_t)m[h] * pitch + x_unit(u[h] >> 4, (u[h] >> 2) & 3u, u[h] & 3u)] = o;
+            if (EXACT) {
+                float sum = ((bf16lo(v[h].x) + bf16hi(v[h].x)) + (bf16lo(v[h].y) + bf16hi(v[h].y))) +
+                            ((bf16lo(v[h].z) + bf16hi(v[h].z)) + (bf16lo(v[h].w) + bf16hi(v[h].w)));
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                if (PAIR) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+                if (i[h] < total && (u[h] & 3u) == 0u) xsum[m[h] * cpr + (u[h] >> 2)] = sum;
+            }
+        }
+    }
+}
+
+// One-pass staging for more than four staged rows, for rows short enough that every thread handles one or two
 // units (K <= 2048): a thread loads a unit, stores it permuted, and the 4 (PAIR: 8) lanes that hold
 // a chunk (a 64-weight group) add up its fp32 sum with shuffles, so x is read once and there is
 // one load latency instead of two.  Whole warps iterate (THREADS and the units per row are
 // multiples of 32 resp. 16, so lane groups never straddle a chunk).  For long rows the two-pass
 // version above is faster: its loads are independent across iterations.
 template <int BITS, bool EXACT, int MP, bool PAIR>
-__device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, uint4* xs,
+__device__ __forceinline__ void stage_x_onepass_wide(const uint16_t* __restrict__ x, uint4* xs,
                                                 float* xsum, uint32_t M, uint32_t K,
                                                 uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
     static_assert(BITS == 4, "one-pass staging exists for 4-bit codes only (8-bit x is staged as scaled fp16)");
@@ -201,6 +250,24 @@ __device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, 
 // row) and one column set serves four activation rows.  Used for M = 3, 4 at group 64; the sums
 // of a group's two chunks then meet inside the tensor core instead of after the scale, so a row
 // agrees with its M <= 2 value to fp32 rounding, not bit for bit.
+#ifdef MIORI_TMA_TRACE
+// Profiling build only: %globaltimer marks of the first and the last CTA of the first 256 launches.
+__device__ unsigned long long g_tma_marks[256 * 2 * 8];
+__device__ unsigned int g_tma_launch[4];
+__device__ unsigned long long g_tma_pmarks[256 * 2 * 4];  // the producer thread's marks
+__device__ __forceinline__ unsigned long long gtimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TMA_MARK(i)                                                                              \
+    do {                                                                                         \
+        if (trace_slot < 256u) g_tma_marks[(trace_slot * 2 + trace_which) * 8 + (i)] = gtimer(); \
+    } while (0)
+#else
+#define TMA_MARK(i) do { } while (0)
+#endif
+
 template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR>
 __global__ void __launch_bounds__(THREADS, (NT == 1 && !ROOMY) ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -253,6 +320,13 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     float* kred = red + (size_t)GROUPS * Red<MP>::GROUP_FLOATS;          // [2][GROUPS][16*MP]
 
     pdl_launch_dependents();
+#ifdef MIORI_TMA_TRACE
+    const unsigned int trace_which = blockIdx.x == 0 ? 0u : 1u;
+    unsigned int trace_slot = 0xffffffffu;
+    if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+        trace_slot = atomicAdd(&g_tma_launch[trace_which], 1u);
+    TMA_MARK(0);
+#endif
 
     // This CTA's tiles.  Slabs are enumerated in sets of ngrp tiles (one
     // per active group), k-slab major inside a set, so that consecutive slabs belong to
@@ -263,8 +337,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // When a CTA has fewer tiles than groups and K spans several slabs, kpar groups share a
     // tile: each takes every kpar-th k-slab (a "virtual tile") and their partial outputs are
     // summed in a fixed order at the end.  kslabs is a multiple of kpar.
-    const uint32_t ntiles = ((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) * kpar;  // virtual
-    const uint32_t kslabs_v = kslabs / kpar;
+    const uint32_t kshift = kpar >> 1;  // kpar is 1, 2 or 4: log2 without a division
+    const uint32_t ntiles = ((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) << kshift;  // virtual
+    const uint32_t kslabs_v = kslabs >> kshift;
     const uint32_t total = ntiles * kslabs_v;
         const uint32_t stage_tx = Q_BYTES + 2u * 16u * gps * 2u;  // bytes tiled TMA delivers per slab
 
@@ -275,8 +350,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // p_kmod = k % nsg and p_use = k / nsg for the owning group's slab counter k.
     uint32_t p_set0 = 0, p_ks = 0, p_gi = 0, p_kmod = 0, p_use = 0;
     // issue every slab whose stage is free, without blocking
-    auto try_refill = [&]() {
-        while (issued < total) {
+    auto try_refill = [&](uint32_t upto) {
+        while (issued < upto) {
             const uint32_t stage = p_gi * nsg + p_kmod;
             if (p_use != 0u) {
                 if (!mbar_try(smem_addr(&empty_bars[stage]), (p_use - 1u) & 1u)) break;
@@ -285,8 +360,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint32_t bar = smem_addr(&full_bars[stage]);
             const uint32_t dst = smem_addr(ring + (size_t)stage * STAGE_BYTES);
             const uint32_t vt = p_set0 + p_gi;
-            const uint32_t row = (blockIdx.x + (vt / kpar) * gridDim.x) * 16u;
-            const uint32_t ks = vt % kpar + p_ks * kpar;
+            const uint32_t row = (blockIdx.x + (vt >> kshift) * gridDim.x) * 16u;
+            const uint32_t ks = (vt & (kpar - 1u)) + (p_ks << kshift);
             if (linear) {
                 const uint32_t nrows = min(16u, N - row);  // rows past N keep stale (unused) data
                 mbar_expect_tx(bar, nrows * (qpitch + 4u * spitch));
@@ -312,6 +387,14 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     const bool producer = threadIdx.x == WARPS * 32;
     if (producer) {
+#ifdef MIORI_TMA_TRACE
+        unsigned int pslot = 0xffffffffu;
+        if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) pslot = atomicAdd(&g_tma_launch[2 + trace_which], 1u);
+#define TMA_PMARK(i) do { if (pslot < 256u) g_tma_pmarks[(pslot * 2 + trace_which) * 4 + (i)] = gtimer(); } while (0)
+        TMA_PMARK(0);
+#else
+#define TMA_PMARK(i) do { } while (0)
+#endif
         abort_flag = 0u;
         x_maxbits[0] = x_maxbits[1] = x_maxbits[2] = x_maxbits[3] = 0u;
         for (uint32_t i = 0; i < nstage; ++i) {
@@ -319,10 +402,17 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(smem_addr(&empty_bars[i]), 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        try_refill();  // fills the rings: up to nstage slabs in flight before the wait
+        TMA_PMARK(1);
+        try_refill(total);  // fills the rings: up to nstage slabs in flight before the wait
+        TMA_PMARK(2);
+#ifdef MIORI_TMA_TRACE
+        for (int spin = 0; spin < 100000 && !mbar_try(smem_addr(&full_bars[0]), 0u); ++spin) { }
+        TMA_PMARK(3);
+#endif
     }
 
     pdl_wait_prior();  // x (and y) belong to the predecessor until here
+    TMA_MARK(1);
 
     // N-sharded launch (pa.world > 1): this rank's rows [row0, row0 + N) of an n_total-row output
     // go into its own y (at user offset y_off of its arena) and, as {value, launch number}
@@ -383,8 +473,13 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
     bool staged = false;
     if constexpr (BITS == 4) {
-        if ((ROOMY || MP <= 2) && kslabs == 1u) {
-            stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+        if constexpr (MP <= 4) {
+            if (ROOMY || MP <= 2) {
+                stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+                staged = true;
+            }
+        } else if ((ROOMY || MP <= 2) && kslabs == 1u) {
+            stage_x_onepass_wide<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
             staged = true;
         }
     }
@@ -392,6 +487,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
+    TMA_MARK(2);
 
     // per-lane constants, all as 32-bit shared addresses / byte offsets
     const uint32_t n = lane >> 2;
@@ -429,7 +525,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // keep the rings fed until every slab has been issued (bounded: gives up with the CTA)
         const long long t0 = clock64();
         while (issued < total && !abort_flag) {
-            try_refill();
+            try_refill(total);
             if (clock64() - t0 > 4 * WAIT_LIMIT_CYCLES) {
                 abort_flag = 1u;
                 device_error(0x6E14u, blockIdx.x, issued);
@@ -440,21 +536,27 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t nt = min(ngrp, ntiles - set0);
         if (grp >= nt) break;
         const uint32_t vt = set0 + grp;
-        const uint32_t kp = kpar > 1u ? vt % kpar : 0u;
-        const uint32_t tile = blockIdx.x + (kpar > 1u ? vt / kpar : vt) * gridDim.x;
+        const uint32_t kp = vt & (kpar - 1u);
+        const uint32_t tile = blockIdx.x + (vt >> kshift) * gridDim.x;
         // start at this group's first k-slab of the row
         if (kpar > 1u) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xb[j] += kp * (xadv[j] / kpar);
+            for (int j = 0; j < NT; ++j) xb[j] += kp * (xadv[j] >> kshift);
             xsp += kp * 256u;
         }
         for (uint32_t ks = 0; ks < kslabs_v; ++ks) {
             const uint32_t stage = grp * nsg + c_kmod, parity = c_par;
             if (++c_kmod == nsg) { c_kmod = 0; c_par ^= 1u; }
+#ifdef MIORI_TMA_TRACE
+            if (tile_it == 0 && ks == 0) TMA_MARK(7);
+#endif
             if (ok) {
                 ok = mbar_wait(smem_addr(&full_bars[stage]), parity, &abort_flag, 0x10);
                 ok = __all_sync(0xFFFFFFFFu, ok);
             }
+#ifdef MIORI_TMA_TRACE
+            if (tile_it == 0 && ks == 0) TMA_MARK(4);
+#endif
             if (ok) {
                 const uint32_t st = ring_a + stage * (uint32_t)STAGE_BYTES;
                 uint32_t qa = st + q_lane, sa = st + sb_lane, lc = lc0;
@@ -566,9 +668,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         // back to k-slab 0 of the row
 #pragma unroll
-        for (int j = 0; j < NT; ++j) xb[j] -= kslabs_v * xadv[j] + (kpar > 1u ? kp * (xadv[j] / kpar) : 0u);
-        xsp -= kslabs_v * xs_adv + (kpar > 1u ? kp * 256u : 0u);
+        for (int j = 0; j < NT; ++j) xb[j] -= kslabs_v * xadv[j] + kp * (xadv[j] >> kshift);
+        xsp -= kslabs_v * xs_adv + kp * 256u;
 
+#ifdef MIORI_TMA_TRACE
+        if (tile_it == 0) TMA_MARK(5);
+#endif
         // ---- tile complete: quad sum (EXACT), then 4 partials per output through shared memory
         constexpr int WS = Red<MP>::WS;
         float* buf = gred + (size_t)(tile_it & 1u) * 4 * WS;
@@ -630,7 +735,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         if (kpar > 1u) {
             // the kpar groups of this tile meet; the first of them sums the partials in order
-            named_barrier(5u + grp / kpar, kpar * 128u);
+            named_barrier(5u + (grp >> kshift), kpar * 128u);
             if (kp == 0u) {
                 const float* kr = kred + ((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP);
                 for (uint32_t o = gt; o < 16u * MP; o += 128u) {
@@ -641,11 +746,15 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
             }
         }
+#ifdef MIORI_TMA_TRACE
+        if (tile_it == 0) TMA_MARK(6);
+#endif
         ++tile_it;
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
     }
 
+    TMA_MARK(3);
     if (abort_flag) {  // let copies still in flight land before the CTA's memory is released
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
@@ -685,26 +794,38 @@ struct Shard {
 // take the problem.
 struct Plan {
     uint32_t grid, ngrp, nsg, kpar;
+    bool pad = false;  // raise the shared-memory request above half an SM (see plan_stages)
     bool roomy;  // one CTA per SM and few tiles: use the instantiation with the larger register budget
 };
 template <int BITS, bool EXACT, int NT, bool PAIR>
 Plan plan_stages(uint32_t N, uint32_t K, uint32_t group) {
     constexpr int KC = 16 * 4 * (128 / BITS);
-    Plan p = {0, 0, 0, 1, false};
+    Plan p = {0, 0, 0, 1, false, false};
     if ((K / group) % 8 != 0) return p;  // scale rows must have a 16-byte pitch for TMA
     const size_t fixed = fixed_smem<BITS, EXACT, NT, PAIR>(K);
     const uint32_t tiles = (N + 15) / 16, kslabs = (K + KC - 1) / KC;
     const uint32_t sms = (uint32_t)sm_count();
-    // A CTA is sized for half an SM (shared memory and, for M <= 2 / 5..8, registers).  Short
-    // kernels launch one CTA per SM so that the next kernel of a dependent-launch chain can be
-    // resident beside it and prefetch; long ones launch two per SM for latency hiding.
+    // Long streams (many tiles per SM) launch two CTAs per SM, each sized for half an SM, for
+    // latency hiding.  Everything else launches at most one CTA per SM, and the one- and two-row
+    // kernels then also claim more than half of the SM's shared memory, so that no second CTA of
+    // any kernel of this family can join it.  Sharing an SM with the successor of a
+    // dependent-launch chain looks attractive (it prefetches while this one computes) and is
+    // 5-10 % faster while every launch has the same footprint, but the placement is not stable:
+    // after a launch with another footprint the successor's CTAs double up on the SMs that were
+    // free and leave others without one, every later launch inherits the skew, and a 24-layer
+    // chain of four shapes ran 17 % slower than the sum of its parts.  With the SM to itself a CTA
+    // starts as its predecessor's CTA exits, fills a ring of up to 200 KB during the ~1.5 us
+    // hand-over between the grids, and the placement is one CTA per SM whatever ran before.
     const size_t half = 112 * 1024, hard = 208 * 1024;
     const bool fits_half = fixed + 4 * STAGE_BYTES <= half;
     if (!fits_half && fixed + 2 * STAGE_BYTES > hard) return p;
-    const uint32_t st = (uint32_t)(((fits_half ? half : hard) - fixed) / STAGE_BYTES);
-    const bool two_per_sm = fits_half && NT == 1 && tiles * kslabs > 8 * sms;
+    const bool two_per_sm = fits_half && NT == 1 && tiles * kslabs > 6 * sms;
+    const bool alone = !two_per_sm && EXACT && NT == 1 && !PAIR;
+    const bool whole = !fits_half || alone;
+    const uint32_t st = (uint32_t)(((whole ? hard : half) - fixed) / STAGE_BYTES);
     p.grid = std::min<uint32_t>(tiles, two_per_sm ? 2 * sms : sms);
-    p.roomy = !two_per_sm && tiles <= 2 * sms;
+    p.roomy = !two_per_sm && (tiles <= 2 * sms || alone);
+    p.pad = alone;
     const uint32_t tiles_cta = (tiles + p.grid - 1) / p.grid;  // tiles of the busiest CTA
     // few tiles per CTA and a long K: let 2 or 4 groups share a tile, each taking every
     // kpar-th k-slab
@@ -748,16 +869,17 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
         auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR>              \
                           : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR>;               \
         e = cudaSuccess;                                                                         \
-        if (smem > 48 * 1024)                                                                    \
-            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (smem_l > 48 * 1024)                                                                  \
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_l); \
         if (e == cudaSuccess)                                                                    \
-            e = launch(kern, dim3(grid), dim3(THREADS), smem, stream, pdl, tq, ts, tb, ql,       \
+            e = launch(kern, dim3(grid), dim3(THREADS), smem_l, stream, pdl, tq, ts, tb, ql,     \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
                        reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
                        sh.pa, sh.pa.world > 1 ? sh.n_total : N, sh.pa.world > 1 ? sh.row0 : 0u, sh.y_off); \
     } while (0)
     const bool sharded = sh.pa.world > 1;
     const bool roomy = NT == 1 && plan.roomy;
+    const size_t smem_l = plan.pad ? std::max<size_t>(smem, 120 * 1024) : smem;
     if (flags & MIORI_OUT_BF16) {
         if (sharded) MIORI_TMA_LAUNCH(true, true); else MIORI_TMA_LAUNCH(true, false);
     } else {
@@ -782,9 +904,10 @@ int try_launch(const void* q, const void* s, const void* b, const void* x, void*
     } while (0)
     if (M <= 2) MIORI_TMA_TRY(true, 1, false);
     if constexpr (BITS == 4) {
-        // three and four rows at group 64: one column set instead of two (13-21 % faster); one
-        // and two rows stay on the per-chunk columns, which stage half as much x
-        if (M <= 4 && group == 64) MIORI_TMA_TRY(true, 1, true);
+        // three and four rows at group 64: one column set instead of two (13-21 % faster while K
+        // fits one slab; over several slabs the two column sets measured 7-12 % faster); one and
+        // two rows stay on the per-chunk columns, which stage half as much x
+        if (M <= 4 && group == 64 && K <= 2048) MIORI_TMA_TRY(true, 1, true);
     }
     if (M <= 4) MIORI_TMA_TRY(true, 2, false);
     if constexpr (BITS == 8) {

@@ -169,6 +169,15 @@ MIORI_API int miori_device_error_poll(void) {
     return (int)rec[0];
 }
 
+#ifdef MIORI_TMA_TRACE
+// Profiling build only: read and reset the TMA GEMV's %globaltimer marks.
+MIORI_API int miori_debug_tma_marks(unsigned long long* out4096) {
+    if (cudaMemcpyFromSymbol(out4096, gemvtma::g_tma_marks, 4096 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(out4096 + 4096, gemvtma::g_tma_pmarks, 2048 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    return cudaMemcpyToSymbol(gemvtma::g_tma_launch, zero, sizeof(zero)) == cudaSuccess ? 0 : -1;
+}
+#endif
 #ifdef MIORI_UMMA_TRACE
 // Profiling build only: read and clear the tcgen05 GEMV's cycle counters.
 MIORI_API int miori_debug_umma_trace(long long* out32) {
