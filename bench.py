@@ -353,6 +353,12 @@ def main():
         rows = N // world
         return t[rank * rows:(rank + 1) * rows]
 
+    def my_cache_rows(cache, N, K):
+        # the bf16 cache is flat; rows are stored one after the other (a promise of the header)
+        rows = N // world
+        lo, hi = lib.miori_cache_bytes(rank * rows, K) // 2, lib.miori_cache_bytes((rank + 1) * rows, K) // 2
+        return cache[lo:hi]
+
     stack = []
     for l in range(layers):
         projs = []
@@ -428,7 +434,7 @@ def main():
         if not do_split:
             miori_b200.linear4(q, s, b, cache, x, group=G, flags=pdl, out=y_loc[M][i], workspace=ws)
             return
-        q, s, b, cache = my_rows(q, N), my_rows(s, N), my_rows(b, N), my_rows(cache, N)
+        q, s, b, cache = my_rows(q, N), my_rows(s, N), my_rows(b, N), my_cache_rows(cache, N, K)
         if grp is not None and packed_path(M, K):
             grp.gemv_allgather(4, q, s, b, x, y_off[M][i], rank * (N // world), N, group=G, flags=pdl)
             return
@@ -459,7 +465,7 @@ def main():
                 part = tuple(my_rows(t, N) for t in full)
                 x = x_dev[M][i]
                 want = miori_b200.linear4(*full, caches[-1][i], x, group=G, workspace=ws)
-                c_part = my_rows(caches[-1][i], N)
+                c_part = my_cache_rows(caches[-1][i], N, K)
                 rows = N // world
                 if grp is not None and packed_path(M, K):
                     grp.gemv_allgather(4, *part, x, tmp_off[i], rank * rows, N, group=G, flags=pdl)

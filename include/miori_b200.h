@@ -119,7 +119,10 @@ int miori_dequant8_rowmajor(const void* q, const void* s, const void* b, void* o
                             uint32_t N, uint32_t K, uint32_t group, void* stream);
 /* The cache consumed by miori_gemm_bf16_cache.  Its layout is private to this library
  * (as [N/64][K][64] is private to the reference's dequant_tile / gemm_mpp pair);
- * miori_cache_bytes gives its size and miori_cache_to_rowmajor undoes the layout. */
+ * miori_cache_bytes gives its size and miori_cache_to_rowmajor undoes the layout.  One promise
+ * is public: weight rows are stored one after the other, so bytes [miori_cache_bytes(r0, K),
+ * miori_cache_bytes(r0 + n, K)) of a cache are the cache of its rows r0 .. r0 + n - 1, and a
+ * row shard of a projection needs no copy. */
 size_t miori_cache_bytes(uint32_t N, uint32_t K);
 int miori_dequant4_cache(const void* q, const void* s, const void* b, void* cache,
                          uint32_t N, uint32_t K, uint32_t group, void* stream);

@@ -105,19 +105,62 @@ embed8_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ s, const
 }
 
 // Largest element of a vector and its index (ties: the lowest index, as the host loop of
-// src/engine.cpp:740-747 finds it).  One CTA; 1024 threads walk the vector, then reduce.
+// src/engine.cpp:740-747 finds it).  A thread-block cluster of up to 8 CTAs shares the vector:
+// 16-byte loads, a shuffle and shared-memory reduction per CTA, then every CTA hands its
+// candidate to CTA 0 through distributed shared memory and CTA 0's first thread holds the result.
 struct Best {
     float v;
     uint32_t i;
 };
+constexpr int ARGMAX_THREADS = 1024, ARGMAX_CLUSTER = 8;
 __device__ __forceinline__ Best better(Best a, Best b) {
     return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// This CTA's best over its slice of v[0, n): elements are compared in index order inside a thread
+// and ties across threads go to the lower index, so the result is the first maximum.
 template <bool BF16>
 __device__ __forceinline__ Best block_argmax(const void* __restrict__ v, uint32_t n, uint32_t index0,
                                              Best* warp_best) {
+    constexpr uint32_t PER = BF16 ? 8u : 4u;  // elements per 16-byte load
+    const uint32_t nct = cluster_nctarank(), cr = cluster_ctarank();
+    // slices of whole 16-byte pieces; the last CTA also takes the ragged tail
+    const uint32_t pieces = n / PER, per_cta = (pieces + nct - 1u) / nct;
+    const uint32_t p0 = min(cr * per_cta, pieces), p1 = min(p0 + per_cta, pieces);
     Best me = {-INFINITY, 0xFFFFFFFFu};
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(v) & 15u) == 0;
+    if (vec_ok) {
+        const uint4* v4 = static_cast<const uint4*>(v);
+        for (uint32_t p = p0 + threadIdx.x; p < p1; p += blockDim.x) {
+            const uint4 w = __ldg(v4 + p);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            const uint32_t i0 = index0 + p * PER;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (BF16) {
+                    me = better(me, Best{bf16lo(ww[k]), i0 + 2u * k});
+                    me = better(me, Best{bf16hi(ww[k]), i0 + 2u * k + 1u});
+                } else {
+                    me = better(me, Best{__uint_as_float(ww[k]), i0 + (uint32_t)k});
+                }
+            }
+        }
+    }
+    // scalar part: everything when v is not 16-byte aligned (CTA 0 of the cluster walks it all),
+    // else the tail past the last whole piece (last CTA)
+    uint32_t s0 = n, s1 = n;
+    if (!vec_ok) { if (cr == 0u) s0 = 0u; }
+    else if (cr == nct - 1u) s0 = pieces * PER;
+    for (uint32_t i = s0 + threadIdx.x; i < s1; i += blockDim.x) {
         const float f = BF16 ? bf16_bits_to_float(static_cast<const uint16_t*>(v)[i])
                              : static_cast<const float*>(v)[i];
         me = better(me, Best{f, index0 + i});
@@ -135,18 +178,69 @@ __device__ __forceinline__ Best block_argmax(const void* __restrict__ v, uint32_
     for (uint32_t w = 1; w < blockDim.x / 32u; ++w) all = better(all, warp_best[w]);
     return all;
 }
+// Cluster-wide result, valid in thread 0 of CTA 0 of the cluster.  Every thread of every CTA of
+// the cluster must call it (it contains cluster barriers).  cta_best: ARGMAX_CLUSTER entries of
+// shared memory, at the same offset in every CTA.
 template <bool BF16>
-__global__ void __launch_bounds__(1024)
+__device__ __forceinline__ Best cluster_argmax(const void* __restrict__ v, uint32_t n, uint32_t index0,
+                                               Best* warp_best, Best* cta_best) {
+    const Best mine = block_argmax<BF16>(v, n, index0, warp_best);
+    const uint32_t nct = cluster_nctarank(), cr = cluster_ctarank();
+    if (nct == 1u) return mine;
+    if (threadIdx.x == 0) {
+        uint32_t remote;  // cta_best[cr] in CTA 0's shared memory
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(smem_addr(cta_best + cr)));
+        asm volatile("st.shared::cluster.v2.u32 [%0], {%1, %2};" ::"r"(remote), "r"(__float_as_uint(mine.v)), "r"(mine.i)
+                     : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    Best all = mine;
+    if (cr == 0u && threadIdx.x == 0)
+        for (uint32_t c = 1; c < nct; ++c) all = better(all, cta_best[c]);
+    return all;
+}
+template <bool BF16>
+__global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const void* __restrict__ v, uint32_t n, uint32_t index0, uint32_t* __restrict__ out_index,
               float* __restrict__ out_value) {
     __shared__ Best warp_best[32];
+    __shared__ __align__(8) Best cta_best[ARGMAX_CLUSTER];
     pdl_launch_dependents();
     pdl_wait_prior();
-    const Best all = block_argmax<BF16>(v, n, index0, warp_best);
-    if (threadIdx.x == 0) {
+    const Best all = cluster_argmax<BF16>(v, n, index0, warp_best, cta_best);
+    if (cluster_ctarank() == 0u && threadIdx.x == 0) {
         *out_index = all.i;
         if (out_value) *out_value = all.v;
     }
+}
+// CTAs for a vector of n elements: one per 8192 elements, at most a cluster of 8.
+inline unsigned argmax_ctas(uint32_t n) {
+    const unsigned c = (n + 8191u) / 8192u;
+    return c >= 8u ? 8u : c >= 4u ? 4u : c >= 2u ? 2u : 1u;
+}
+// Launch with `ctas` CTAs forming one cluster.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_cluster(void (*kernel)(KArgs...), unsigned ctas, unsigned threads, cudaStream_t stream,
+                                  bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = ctas;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace neighbors
@@ -211,13 +305,15 @@ MIORI_API int miori_argmax(const void* v, uint32_t n, uint32_t flags, void* out_
     if (n == 0) return fail(MIORI_E_INVALID, "miori_argmax: empty vector");
     cudaError_t e;
     if (flags & MIORI_OUT_BF16)
-        e = launch(neighbors::argmax_kernel<true>, dim3(1), dim3(1024), 0, (cudaStream_t)stream,
-                   (flags & MIORI_LAUNCH_PDL) != 0, v, n, 0u, static_cast<uint32_t*>(out_index),
-                   static_cast<float*>(out_value));
+        e = neighbors::launch_cluster(neighbors::argmax_kernel<true>, neighbors::argmax_ctas(n),
+                                      neighbors::ARGMAX_THREADS, (cudaStream_t)stream,
+                                      (flags & MIORI_LAUNCH_PDL) != 0, v, n, 0u, static_cast<uint32_t*>(out_index),
+                                      static_cast<float*>(out_value));
     else
-        e = launch(neighbors::argmax_kernel<false>, dim3(1), dim3(1024), 0, (cudaStream_t)stream,
-                   (flags & MIORI_LAUNCH_PDL) != 0, v, n, 0u, static_cast<uint32_t*>(out_index),
-                   static_cast<float*>(out_value));
+        e = neighbors::launch_cluster(neighbors::argmax_kernel<false>, neighbors::argmax_ctas(n),
+                                      neighbors::ARGMAX_THREADS, (cudaStream_t)stream,
+                                      (flags & MIORI_LAUNCH_PDL) != 0, v, n, 0u, static_cast<uint32_t*>(out_index),
+                                      static_cast<float*>(out_value));
     if (e != cudaSuccess) return cuda_fail(e, "miori_argmax launch");
     return MIORI_OK;
 }

@@ -57,17 +57,19 @@ allgather_kernel(const PeerArgs pa, const uint8_t* __restrict__ src, uint32_t sr
 // Greedy sampling over an N-sharded head without gathering the logits: every rank finds the best
 // of its own slice, the ranks exchange (value, index) pairs -- two 8-byte packets per rank instead
 // of the whole vector -- and every rank reduces the pairs the same way (ties: lowest index, as the
-// host loop of src/engine.cpp:740-747).  One CTA.  The pairs land in the arena at y_off as
+// host loop of src/engine.cpp:740-747).  One cluster of up to 8 CTAs finds the local best; thread
+// 0 of its first CTA does the exchange.  The pairs land in the arena at y_off as
 // [rank][value, index] followed by the winner [value, index].
 template <bool BF16>
 __global__ void __launch_bounds__(1024)
 argmax_allreduce_kernel(const PeerArgs pa, const void* __restrict__ v, uint32_t n_local, uint32_t index0,
                         size_t y_off) {
     __shared__ neighbors::Best warp_best[32];
+    __shared__ __align__(8) neighbors::Best cta_best[neighbors::ARGMAX_CLUSTER];
     pdl_launch_dependents();
     pdl_wait_prior();
-    const neighbors::Best mine = neighbors::block_argmax<BF16>(v, n_local, index0, warp_best);
-    if (threadIdx.x == 0) {
+    const neighbors::Best mine = neighbors::cluster_argmax<BF16>(v, n_local, index0, warp_best, cta_best);
+    if (neighbors::cluster_ctarank() == 0u && threadIdx.x == 0) {
         uint32_t* y = reinterpret_cast<uint32_t*>(pa.local + PEER_CTL_BYTES + y_off);
         const size_t base = y_off / 4u;
         const uint32_t world = pa.world > 1u ? pa.world : 1u, rank = pa.world > 1u ? pa.rank : 0u;
@@ -96,7 +98,7 @@ argmax_allreduce_kernel(const PeerArgs pa, const void* __restrict__ v, uint32_t 
                 }
                 if (ok) all = neighbors::better(all, b);
             }
-            peer_finish(pa, e);
+            peer_finish_single(pa, e);
         }
         y[2u * world] = __float_as_uint(all.v);
         y[2u * world + 1u] = all.i;
@@ -354,11 +356,13 @@ MIORI_API int miori_argmax_allreduce(miori_peers* g, const void* v, uint32_t n_l
     const bool pdl = (flags & MIORI_LAUNCH_PDL) != 0;
     cudaError_t e;
     if (flags & MIORI_OUT_BF16)
-        e = launch(peers::argmax_allreduce_kernel<true>, dim3(1), dim3(1024), 0, (cudaStream_t)stream, pdl, pa, v,
-                   n_local, index0, y_offset);
+        e = neighbors::launch_cluster(peers::argmax_allreduce_kernel<true>, neighbors::argmax_ctas(n_local),
+                                      neighbors::ARGMAX_THREADS, (cudaStream_t)stream, pdl, pa, v, n_local, index0,
+                                      y_offset);
     else
-        e = launch(peers::argmax_allreduce_kernel<false>, dim3(1), dim3(1024), 0, (cudaStream_t)stream, pdl, pa, v,
-                   n_local, index0, y_offset);
+        e = neighbors::launch_cluster(peers::argmax_allreduce_kernel<false>, neighbors::argmax_ctas(n_local),
+                                      neighbors::ARGMAX_THREADS, (cudaStream_t)stream, pdl, pa, v, n_local, index0,
+                                      y_offset);
     if (e != cudaSuccess) return cuda_fail(e, "miori_argmax_allreduce launch");
     return MIORI_OK;
 }

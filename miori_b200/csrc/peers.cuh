@@ -127,6 +127,12 @@ __device__ __forceinline__ void peer_finish(const PeerArgs& pa, uint32_t e) {
     ctl[CTL_COUNT] = 0u;
     st_relaxed_sys(ctl + CTL_EPOCH, e);
 }
+// The same for a kernel in which a single thread of the whole grid does the peer work: that
+// thread advances the launch number itself.
+__device__ __forceinline__ void peer_finish_single(const PeerArgs& pa, uint32_t e) {
+    __threadfence();
+    st_relaxed_sys(peer_ctl(pa) + CTL_EPOCH, e);
+}
 #endif
 
 }  // namespace miori_b200

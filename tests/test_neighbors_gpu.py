@@ -83,6 +83,25 @@ def test_argmax_ties_go_to_the_lowest_index():
     assert int(idx.item()) == int(np.argmax(vb.float().numpy())) and float(val.item()) == float(vb.float().max())
 
 
+@pytest.mark.parametrize("n", [1, 7, 33, 8191, 8192, 8200, 20001, 65536, 131077])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_argmax_sizes_and_alignment(n, dtype):
+    """Every cluster size (1, 2, 4, 8 CTAs), ragged tails, a maximum in the last element, and a
+    vector that does not start on a 16-byte boundary (scalar loads then)."""
+    g = torch.Generator().manual_seed(n)
+    v = torch.randn(n + 3, generator=g).to(dtype)
+    for shift in (0, 1):   # 1: the view starts 2 or 4 bytes into the allocation
+        w = v[shift:shift + n].clone()
+        for spot in (None, n - 1, 0, n // 2):
+            if spot is not None:
+                w[spot] = 50.0 + (spot % 7)
+            dv = v.to(DEV)
+            dv[shift:shift + n] = w.to(DEV)
+            idx, val = miori_b200.argmax(dv[shift:shift + n])
+            want = int(np.argmax(w.float().numpy()))
+            assert int(idx.item()) == want and float(val.item()) == float(w.float()[want]), (n, dtype, shift, spot)
+
+
 @pytest.mark.parametrize("bits,N,K,M,group", [(4, 2048, 2048, 1, 64), (4, 3072, 2048, 4, 32), (4, 640, 2048, 8, 64),
                                               (8, 1024, 2048, 2, 64), (4, 2048, 8192, 1, 64), (4, 1536, 2048, 32, 64)])
 def test_gemv_with_fused_rmsnorm(port, bits, N, K, M, group):
