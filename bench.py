@@ -653,9 +653,10 @@ def main():
     peaks, peak_kind = measured_peaks()
     m1 = per_m["1"]
     # DRAM bytes (read + write) per algorithmic byte of gemv_tma_kernel, from an ncu capture of
-    # the N=131072, K=2048, M=1 case (156.1 MB moved for 151.0 MB of weights); traffic grows in
-    # proportion to the weights a launch streams
-    DRAM_PER_ALGO_BYTE = 1.034
+    # the N=8192, K=2048, M=1 launch over a pool larger than L2 (9.465 MB read, nothing written --
+    # the 32 KB of y stay in L2 -- for 9.437 MB of weights); traffic grows in proportion to the
+    # weights a launch streams
+    DRAM_PER_ALGO_BYTE = 1.003
     roofline = {
         "kernel": "gemv_tma_kernel<4,exact,1> (M=1 pass of the stack, 96 launches per pass)",
         "bound": "hbm", "achieved": m1["gbs"] / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
