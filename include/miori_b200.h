@@ -140,6 +140,13 @@ int miori_cache_to_rowmajor(const void* cache, void* out, uint32_t N, uint32_t K
 int miori_gemm_bf16_cache(const void* A, const void* cache, void* C, uint32_t M, uint32_t N,
                           uint32_t K, uint32_t flags, void* stream);
 
+/* Host-only: what the planner would launch for this shape with `workspace_bytes` of workspace --
+ * the tile's width in output columns (128 or 256; a tile is 128 rows, 256 when two CTAs share it),
+ * the CTAs per tile (1, or 2 for the cta_group::2 kernel) and the number of K slices (1 = no
+ * split).  For tests and for hosts that want to log the choice; no device is touched beyond the
+ * SM count. */
+int miori_gemm_plan(uint32_t M, uint32_t N, uint32_t K, size_t workspace_bytes, uint32_t* tile_n,
+                    uint32_t* ctas_per_tile, uint32_t* splits);
 /* Same product with a caller-provided scratch area that lets problems with few output tiles
  * (small M or N, long K) split K across SMs: partial tiles go to `workspace` (fp32) and a
  * second kernel sums them in a fixed order, so results stay reproducible and independent of

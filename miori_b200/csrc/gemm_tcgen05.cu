@@ -767,9 +767,11 @@ static GemmPlan plan_gemm(uint32_t M, uint32_t N, uint32_t K, uint32_t flags, si
     else if (mn) max_s = (uint32_t)std::min<size_t>(max_s, std::max<size_t>(1, ws_bytes / (mn * 4)));
     GemmPlan best = {false, false, 1};
     double best_t = 1e30;
+    const uint32_t force_split = (flags >> MIORI_TUNE_GEMM_SPLIT_SHIFT) & 15u;
     for (const Shape& sh : shapes) {
         if (!sh.allowed) continue;
         for (uint32_t sp = 1; sp <= max_s; ++sp) {
+            if (force_split && sp != std::min(force_split, max_s)) continue;
             const uint32_t waves = (sh.tiles * sp + sh.units - 1) / sh.units;
             double t = (double)waves * ((k_blocks + sp - 1) / sp) * sh.t_kb;
             if (t < t_hbm) t = t_hbm;
@@ -959,6 +961,16 @@ MIORI_API int miori_gemm_bf16_cache_static(const void* A, const void* cache, voi
     // every element of every partial slice is written by the GEMM before the reduction reads
     // it, so the previous call's contents never need clearing
     return gemm::run_plan(want, A, cache, Cm, M, N, K, flags, ws, (cudaStream_t)stream);
+}
+
+MIORI_API int miori_gemm_plan(uint32_t M, uint32_t N, uint32_t K, size_t workspace_bytes, uint32_t* tile_n,
+                              uint32_t* ctas_per_tile, uint32_t* splits) {
+    if (M == 0 || N == 0 || K == 0) return fail(MIORI_E_INVALID, "miori_gemm_plan: empty shape");
+    const gemm::GemmPlan p = gemm::plan_gemm(M, N, K, 0, workspace_bytes);
+    if (tile_n) *tile_n = (p.wide || p.pair) ? 256u : 128u;
+    if (ctas_per_tile) *ctas_per_tile = p.pair ? 2u : 1u;
+    if (splits) *splits = p.splits;
+    return MIORI_OK;
 }
 
 MIORI_API size_t miori_gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K) {

@@ -11,4 +11,5 @@
 #define MIORI_TUNE_GEMM_PAIR 0x4000u    // GEMM: two-CTA (cta_group::2) kernel
 #define MIORI_TUNE_GEMM_NOPAIR 0x8000u  // GEMM: never the two-CTA kernel
 #define MIORI_TUNE_UMMA_SPLIT_SHIFT 16  // GEMV (tcgen05 kernel): bits 16..19 = forced K split (1, 2, 4, 8)
+#define MIORI_TUNE_GEMM_SPLIT_SHIFT 16  // GEMM: bits 16..19 = forced K split count (1..15; needs the workspace for it)
 #define MIORI_TUNE_GEMV_UMMA 0x100000u  // GEMV: the tcgen05 kernel even where the heuristics prefer another

@@ -44,7 +44,7 @@ def test_golden_fixture(path):
     assert_close(y, g["y"], rel_max=TOL_EXACT_PATH, what=path)
 
 
-# the reference model's projection shapes (config/m6.h) and BASELINE's synthetic ones
+# the reference model's projection shapes (config/m6.h) and the benchmark's synthetic ones
 SHAPES4 = [(2048, 2048), (512, 2048), (16, 2048), (6144, 2048), (7680, 2048), (2048, 7680),
            (8192, 2048), (3072, 2048), (2048, 8192), (1, 32), (17, 64), (130, 96)]
 
