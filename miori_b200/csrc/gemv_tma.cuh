@@ -766,6 +766,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             peer_collect<OUT_BF16>(pa, e, y_off, M, n_total, row0, N);
             __syncthreads();
             if (threadIdx.x == 0) peer_finish(pa, e);
+            TMA_MARK(7);  // tracing build: the peers' rows are in y
         }
     }
 }
