@@ -424,8 +424,11 @@ def main():
                    for M in M_SWEEP for N, K in SHAPES for rows in (N, N // world))
     ws = torch.empty(max(ws_bytes // 4, 4), dtype=torch.float32, device=dev)
 
-    def packed_path(M, K):  # miori_linear4's own rule
+    def packed_path(M, K):  # the packed-weight GEMV has a fast form (and a fused exchange) here
         return M <= 8 or (M <= 16 and K <= 2048)
+
+    def route(M, rows, K):  # miori_linear4's own rule: 0 packed GEMV, 1 narrow-batch cache kernel, 2 GEMM
+        return lib.miori_linear4_route(M, rows, K, 1)
 
     def run_proj(M, i, w, cache, x, do_split):
         """One projection: on this rank's rows with the result gathered everywhere (split), or whole."""
@@ -483,7 +486,7 @@ def main():
                         got = buf.view(world, M, rows).permute(1, 0, 2).reshape(M, N)
                 torch.cuda.synchronize()
                 cases += 1
-                if packed_path(M, K):
+                if M <= 4:  # packed weights on both sides: bit for bit
                     if not torch.equal(got, want):
                         bad.append(f"M={M} N={N} K={K}")
                 else:
@@ -563,11 +566,14 @@ def main():
     def kernels_in_pass(M):  # this library's kernel launches in one pass at M rows, on one rank
         n = 0
         for i, (N, K) in enumerate(SHAPES):
-            if packed_path(M, K):
-                n += 1
+            if split[M][i] and grp is not None and packed_path(M, K):
+                n += 1                                                    # GEMV with the exchange in its epilogue
                 continue
             rows = N // world if split[M][i] else N
-            n += 2 if lib.miori_gemm_workspace_bytes(M, rows, K) else 1   # GEMM (+ K-split sum)
+            if route(M, rows, K) == 2:
+                n += 2 if lib.miori_gemm_workspace_bytes(M, rows, K) else 1   # GEMM (+ K-split sum)
+            else:
+                n += 1
             n += 1 if (grp is not None and split[M][i]) else 0            # peer all-gather
         return layers * n
     say("graphs captured")
@@ -594,9 +600,9 @@ def main():
         ms = timed(graphs[M].replay, max(3, args.steps // 2)) / max(3, args.steps // 2)
         per_m[str(M)] = {"ms_per_pass": ms, "gbs": bytes_pass / (ms * 1e-3) / 1e9,
                          "us_per_launch": 1e3 * ms / launches_pass,
-                         "path": "gemv4 on packed int4" if M <= 8 else
-                         ("gemv4 on packed int4 (K<=2048), tcgen05 GEMM on the bf16 cache (K=8192)"
-                          if M <= 16 else "tcgen05 GEMM on the bf16 cache")}
+                         "path": {f"{K}->{N}": ("packed int4 GEMV", "narrow-batch kernel on the bf16 cache",
+                                                "tcgen05 GEMM on the bf16 cache")[route(M, N, K)]
+                                  for N, K in SHAPES}}
 
     # ---- the same M=1 pass with the four projections of a layer on four concurrent streams
     # (no dependency between them): separates kernel throughput from launch-chain latency

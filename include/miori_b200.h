@@ -196,11 +196,24 @@ int miori_gemm_bf16_strided(const void* A, uint32_t lda, const void* B, uint32_t
  *      (reference src/batch.cpp:223-230, 429-431, src/engine.cpp:508-518), which route a
  *      projection to gemv4_b for narrow batches and to the bf16-cache GEMM otherwise. ------ */
 
-/* y[M][N] (fp32) = x[M][K] (bf16) x W^T.  M <= 8 streams the packed 4-bit weights
- * (miori_gemv4), and so do 9..16 rows when K <= 2048; wider M multiplies the bf16 cache on the
- * tensor cores (miori_gemm_bf16_cache_ws) when `cache` is given, else stays on the packed
- * weights (M <= 32).  The reference's cut-over is 4 rows; here the packed path stays ahead
- * further because it moves a quarter of the bytes. */
+/* y[M][N] = x[M][K] (bf16) x cache[N][K]^T for 1 <= M <= 32: the cache of miori_dequant4_cache
+ * streamed once in 16-row tiles on mma.sync tensor cores, fp32 accumulation, fp32 or bf16 output,
+ * no workspace.  What the reference's wide-batch path (gemm_mpp on the bf16 cache) computes for
+ * the batch sizes of a decode step; a row's value depends neither on M nor on the grid.  Every
+ * warp keeps its share of the activations in registers, which bounds K: K <= 2048 for 17..32 rows,
+ * K <= 4096 for 9..16 rows, K <= 8192 up to 8 rows; beyond that MIORI_E_INVALID: use
+ * miori_gemm_bf16_cache there. */
+int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, uint32_t M, uint32_t N, uint32_t K,
+                          uint32_t flags, void* stream);
+
+/* y[M][N] (fp32) = x[M][K] (bf16) x W^T.  Up to four rows stream the packed 4-bit weights with
+ * fp32 dequantization (miori_gemv4), the reference's own cut-over.  Wider batches multiply the bf16
+ * cache when `cache` is given -- with the narrow-batch kernel (miori_gemv_bf16_cache) while the
+ * projection is short, with the tensor-core GEMM (miori_gemm_bf16_cache_ws) for long rows or wide
+ * outputs at more than 16 rows -- and otherwise stay on the packed weights (as does everything
+ * when no cache is given, M <= 32).  miori_linear4_route tells which: 0 packed GEMV, 1 narrow-batch
+ * cache kernel, 2 tensor-core GEMM (host-only; for logs and tests). */
+int miori_linear4_route(uint32_t M, uint32_t N, uint32_t K, int has_cache);
 int miori_linear4(const void* q, const void* s, const void* b, const void* cache, const void* x,
                   void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
                   void* workspace, size_t workspace_bytes, void* stream);

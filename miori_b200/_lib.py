@@ -51,6 +51,8 @@ _SIGS = {
     "miori_gemm_static_scratch_bytes": (_sz, []),
     "miori_gemm_bf16_cache_static": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
     "miori_gemm_bf16_strided": (_i, [_p, _u32, _p, _u32, _p, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_linear4_route": (_i, [_u32, _u32, _u32, _i]),
+    "miori_gemv_bf16_cache": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
     "miori_gemm_plan": (_i, [_u32, _u32, _u32, _sz, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
     "miori_linear4": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p, _sz, _p]),
     "miori_peers_create": (_i, [_i, _i, _sz, C.POINTER(_p)]),

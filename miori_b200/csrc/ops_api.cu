@@ -5,6 +5,7 @@
 #include "gemv_simt.cuh"
 #include "gemv_tma.cuh"
 #include "gemv_umma.cuh"
+#include "gemv_cache.cuh"
 
 using namespace miori_b200;
 
@@ -108,15 +109,61 @@ MIORI_API int miori_gemv8_rmsnorm(const void* q, const void* s, const void* b, c
     return gemv_rmsnorm_entry<8>("miori_gemv8_rmsnorm", q, s, b, x, gamma, eps, y, N, K, M, group, flags, stream);
 }
 
+MIORI_API int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, uint32_t M, uint32_t N, uint32_t K,
+                                    uint32_t flags, void* stream) {
+    const char* op = "miori_gemv_bf16_cache";
+    if (!x || !cache || !y) return fail(MIORI_E_INVALID, "%s: null pointer", op);
+    if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
+    if (N == 0 || K == 0 || K % 8 != 0)
+        return fail(MIORI_E_INVALID, "%s: N=%u K=%u (K must be a positive multiple of 8)", op, N, K);
+    if (!aligned16(x) || !aligned16(cache) || !aligned16(y))
+        return fail(MIORI_E_INVALID, "%s: x, cache and y must be 16-byte aligned", op);
+    const int rc = gemvcache::try_launch(x, cache, y, M, N, K, flags, (cudaStream_t)stream);
+    if (rc == 1)
+        return fail(MIORI_E_INVALID, "%s: M=%u rows of K=%u are more activations than the kernel keeps in "
+                    "registers (use miori_gemm_bf16_cache)", op, M, K);
+    return rc;
+}
+
+// Where miori_linear4 sends a projection: 0 = packed-weight GEMV, 1 = narrow-batch kernel on the
+// bf16 cache, 2 = tcgen05 GEMM on the bf16 cache.  Measured on B200 in chains of dependent
+// launches (us per launch, 2048 -> 3072 / 2048 -> 2048 / 8192 -> 2048 / 2048 -> 16384):
+//   M = 8:  packed 4.4 / 3.9 / 9.0 / 10.6, narrow 4.1 / 3.2 / 7.7 / 11.8
+//   M = 16: packed 5.4 / 4.7 / 82 / 12.6,  narrow 4.8 / 3.6 / -- / 13.4,  GEMM 8.9 / 7.6 / 12.5 / 15.9
+//   M = 32: packed 10.8 / 7.2 / 162 / 32,  narrow 7.5 / 5.3 / -- / 20.1,  GEMM 8.6 / 7.8 / 12.9 / 15.9
+// Up to four rows stay on the packed weights with fp32 dequantization, as in the reference
+// (src/batch.cpp:223-230 cuts over to the cache above four rows).  Above that the cache is used
+// when given: by the narrow-batch kernel while the projection is short (at most two 16-row tiles
+// per SM: its launch is cheap, but it streams four times the bytes and its mma.sync rate caps it
+// on long streams), else by the packed GEMV while that still has a fast form (up to 16 rows of
+// K <= 2048), else by the tensor-core GEMM.
+static int linear4_route(uint32_t M, uint32_t N, uint32_t K, bool has_cache) {
+    if (M <= 4 || !has_cache) return 0;
+    const uint32_t tiles = (N + 15u) / 16u, slabs = (K + 511u) / 512u;
+    const uint32_t frags = (slabs <= 1 ? 1u : slabs <= 2 ? 2u : slabs <= 4 ? 4u : slabs <= 8 ? 8u : 16u) *
+                           (M <= 8 ? 1u : M <= 16 ? 2u : 4u);
+    if (tiles <= 2u * (uint32_t)sm_count() && slabs <= 16u && frags <= (uint32_t)gemvcache::MAX_FRAGS && K % 8 == 0)
+        return 1;
+    if (M <= 8 || (M <= 16 && K <= 2048)) return 0;
+    return 2;
+}
+
+MIORI_API int miori_linear4_route(uint32_t M, uint32_t N, uint32_t K, int has_cache) {
+    return linear4_route(M, N, K, has_cache != 0);
+}
+
 MIORI_API int miori_linear4(const void* q, const void* s, const void* b, const void* cache,
                             const void* x, void* y, uint32_t N, uint32_t K, uint32_t M,
                             uint32_t group, uint32_t flags, void* workspace, size_t workspace_bytes,
                             void* stream) {
-    // up to 16 rows the packed-weight kernel still wins while the staged activations of a row
-    // fit beside its weight ring (K <= 2048): it reads 0.56 bytes per weight, the cache 2
-    if (M <= 8 || !cache || (M <= 16 && K <= 2048))
+    switch (linear4_route(M, N, K, cache != nullptr)) {
+    case 1:
+        return miori_gemv_bf16_cache(x, cache, y, M, N, K, flags, stream);
+    case 2:
+        return miori_gemm_bf16_cache_ws(x, cache, y, M, N, K, flags, workspace, workspace_bytes, stream);
+    default:
         return miori_gemv4(q, s, b, x, y, N, K, M, group, flags, stream);
-    return miori_gemm_bf16_cache_ws(x, cache, y, M, N, K, flags, workspace, workspace_bytes, stream);
+    }
 }
 
 MIORI_API int miori_dequant4_rowmajor(const void* q, const void* s, const void* b, void* out,

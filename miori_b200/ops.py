@@ -118,9 +118,19 @@ def gemm_bf16_strided(A, B, flags=0, out=None):
     return Cm
 
 
+def gemv_bf16_cache(x, cache, N, flags=0, out=None):
+    """y[M][N] = x[M][K] (bf16) against the bf16 cache, M <= 32: the narrow-batch kernel."""
+    _need_cuda(x, cache)
+    M, K = x.shape
+    dt = torch.bfloat16 if flags & OUT_BF16 else torch.float32
+    y = out if out is not None else torch.empty((M, N), dtype=dt, device=x.device)
+    check(lib.miori_gemv_bf16_cache(x.data_ptr(), cache.data_ptr(), y.data_ptr(), M, N, K, flags, _stream()))
+    return y
+
+
 def linear4(q, s, b, cache, x, group=32, flags=0, out=None, workspace=None):
-    """Projection dispatch (packed-weight GEMV for M <= 8, and M <= 16 while K <= 2048; bf16-cache
-    GEMM above)."""
+    """Projection dispatch: packed-weight GEMV up to four rows, the bf16 cache above (narrow-batch
+    kernel or tensor-core GEMM by shape; lib.miori_linear4_route tells which)."""
     _need_cuda(q, s, b, x)
     M, K = x.shape
     N = q.shape[0]

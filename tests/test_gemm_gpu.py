@@ -127,12 +127,13 @@ def test_split_k_with_workspace_matches_oracle(port, M, N, K):
     assert miori_b200.lib.miori_device_error_poll() == 0
 
 
-@pytest.mark.parametrize("M", [1, 4, 8, 9, 16, 17, 32])
-def test_linear_dispatch(port, M):
-    """miori_linear4 routes narrow batches (M <= 8, and M <= 16 while K <= 2048) to the
-    packed-weight GEMV and wider M to the cache GEMM (the reference's BatchEngine::linear
-    policy, src/batch.cpp:223-230, with a later cut-over)."""
-    N, K = 3072, 2048
+@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 8192), (6144, 2048)])
+@pytest.mark.parametrize("M", [1, 4, 5, 8, 9, 16, 17, 32])
+def test_linear_dispatch(port, M, N, K):
+    """miori_linear4 keeps up to four rows on the packed weights (the reference's cut-over,
+    src/batch.cpp:223-230) and sends wider batches to the bf16 cache -- the narrow-batch kernel or
+    the tensor-core GEMM by shape -- unless no cache is given; miori_linear4_route says which, and
+    the result is that entry's own."""
     q, s, b, cache = _weights(N, K, 64, seed=31)
     x = synth.make_activation(M, K, seed=32, device=DEV)
     ws = miori_b200.gemm_workspace(max(M, 9), N, K, DEV)
@@ -142,8 +143,46 @@ def test_linear_dispatch(port, M):
     want = port.gemv(4, u32(q), u16(s), u16(b), u16(x), 64)
     assert_close(y.cpu().numpy(), want, what=f"linear4 M={M}")
     assert_close(y_nocache.cpu().numpy(), want, what=f"linear4 (no cache) M={M}")
-    if M <= 16:
+    r = miori_b200.lib.miori_linear4_route(M, N, K, 1)
+    assert miori_b200.lib.miori_linear4_route(M, N, K, 0) == 0
+    assert (r == 0) == (M <= 4 or (N == 6144 and (M <= 8 or M <= 16)))
+    if r == 0:
         assert torch.equal(y, miori_b200.gemv4(q, s, b, x, group=64))
+    elif r == 1:
+        assert torch.equal(y, miori_b200.gemv_bf16_cache(x, cache, N))
+    else:
+        assert torch.equal(y, miori_b200.gemm_bf16_cache(x, cache, N, workspace=ws))
+    assert torch.equal(y_nocache, miori_b200.gemv4(q, s, b, x, group=64))
+
+
+@pytest.mark.parametrize("M,N,K", [(32, 2048, 2048), (16, 3072, 2048), (5, 1000, 512), (1, 16, 64), (9, 17, 1096),
+                                   (16, 2048, 4096), (24, 640, 2048), (32, 16384, 2048), (31, 100, 2048),
+                                   (8, 512, 8192), (32, 256, 1536)])
+def test_narrow_batch_cache_kernel(port, M, N, K):
+    """miori_gemv_bf16_cache against the oracle's exact product over the bit-exact cache, with the
+    GEMM's tolerance; a row's value does not depend on M; bf16 output is the rounded fp32 one; a K
+    that is not a multiple of the 512-wide slab is zero-filled, not read past."""
+    Kq = (K + 63) // 64 * 64
+    q, s, b, cache = _weights(N, Kq, 64, seed=M + N + K)
+    rm = ops.cache_to_rowmajor(cache, N, Kq)[:, :K].contiguous()
+    x = synth.make_activation(M, K, seed=7, device=DEV)
+    y = miori_b200.gemv_bf16_cache(x, rm.reshape(-1), N)
+    torch.cuda.synchronize()
+    want = port.gemm_bf16(u16(x), u16(rm))
+    assert_close(y.cpu().numpy(), want, rel_max=1e-4, what=f"narrow batch {M}x{N}x{K}")
+    h = max(1, M // 2)
+    assert torch.equal(miori_b200.gemv_bf16_cache(x[:h].contiguous(), rm.reshape(-1), N), y[:h])
+    assert torch.equal(miori_b200.gemv_bf16_cache(x, rm.reshape(-1), N, flags=miori_b200.OUT_BF16), y.to(torch.bfloat16))
+    assert miori_b200.lib.miori_device_error_poll() == 0
+
+
+def test_narrow_batch_cache_kernel_refuses_what_it_cannot_hold():
+    _, _, _, cache = _weights(64, 8192, 64, seed=3)
+    x = synth.make_activation(16, 8192, seed=4, device=DEV)
+    with pytest.raises(miori_b200.MioriError, match="registers"):
+        miori_b200.gemv_bf16_cache(x, cache, 64)
+    with pytest.raises(miori_b200.MioriError):
+        miori_b200.gemv_bf16_cache(synth.make_activation(33, 64, seed=1, device=DEV), cache, 64)
 
 
 # ---- strided bf16 GEMM (the reference's gemm_naive, shaders/ops.metal:199-251) ---------------
