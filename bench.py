@@ -250,6 +250,13 @@ def run_one(a):
         out = torch.empty((a.n, a.k), dtype=torch.bfloat16, device=dev)
         ms = time_ms(lambda: [miori_b200.dequant4_rowmajor(q, s, b, group=G, out=out) for q, s, b in pool])
         print(f"dequant4 N={a.n} K={a.k}: {ms * 1e3:.2f} us/launch {(wbytes + 2 * a.n * a.k) / ms / 1e6:.0f} GB/s")
+    elif a.one == "gemv_cache":
+        caches = [miori_b200.dequant4_cache(q, s, b, group=G) for q, s, b in pool]
+        del pool
+        y = torch.empty((a.m, a.n), device=dev)
+        ms = time_ms(lambda: [miori_b200.gemv_bf16_cache(x, c, a.n, flags=a.flags, out=y) for c in caches])
+        print(f"gemv_bf16_cache N={a.n} K={a.k} M={a.m}: {ms * 1e3:.2f} us/launch "
+              f"{2.0 * a.n * a.k / ms / 1e6:.0f} GB/s of cache")
     else:
         caches = [miori_b200.dequant4_cache(q, s, b, group=G) for q, s, b in pool]
         del pool
@@ -296,7 +303,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="stack depth (24 is the benchmark)")
     ap.add_argument("--verbose", action="store_true", help="progress on stderr")
     one = ap.add_argument_group("one operator on one GPU (--one): a small case to time or to profile")
-    one.add_argument("--one", choices=["gemv", "gemv_rmsnorm", "gemm", "dequant"])
+    one.add_argument("--one", choices=["gemv", "gemv_rmsnorm", "gemm", "gemv_cache", "dequant"])
     one.add_argument("--bits", type=int, default=4, choices=[4, 8])
     one.add_argument("--n", type=int, default=8192)
     one.add_argument("--k", type=int, default=2048)

@@ -199,7 +199,8 @@ int miori_gemm_bf16_strided(const void* A, uint32_t lda, const void* B, uint32_t
 /* y[M][N] = x[M][K] (bf16) x cache[N][K]^T for 1 <= M <= 32: the cache of miori_dequant4_cache
  * streamed once in 16-row tiles on mma.sync tensor cores, fp32 accumulation, fp32 or bf16 output,
  * no workspace.  What the reference's wide-batch path (gemm_mpp on the bf16 cache) computes for
- * the batch sizes of a decode step; a row's value depends neither on M nor on the grid.  Every
+ * the batch sizes of a decode step; a row's value depends neither on the grid nor on M within a
+ * class of batch sizes (1..8, 9..16, 17..32 rows).  Every
  * warp keeps its share of the activations in registers, which bounds K: K <= 2048 for 17..32 rows,
  * K <= 4096 for 9..16 rows, K <= 8192 up to 8 rows; beyond that MIORI_E_INVALID: use
  * miori_gemm_bf16_cache there. */

@@ -16,15 +16,17 @@
 //     wide: the 64 extra bytes per row make the row pitch 64 (mod 128), which spreads the eight
 //     lanes of a quarter-warp over all bank groups without a swizzle);
 //   * the ring is filled before griddepcontrol.wait (the cache is immutable);
-//   * warp w multiplies k in [32w, 32w + 32) of every stage, for every tile of the CTA.  Its B
+//   * the activation rows come in NT sets of eight (the MMA's columns).  Warp w owns set w % NT
+//     and the k range [32 NT (w / NT), + 32 NT) of every stage, for every tile of the CTA.  Its B
 //     fragments are therefore the same for all tiles and live in REGISTERS: after the wait every
-//     lane loads its 16 bytes of x per (k-slab, set of eight activation rows) straight from global
-//     memory, once -- at most 16 of them, 64 registers -- and x never touches shared memory, which
-//     is left to the ring (eight stages, 139 KB in flight per SM);
-//   * per stage a warp issues two 16-byte loads (the tile's rows g and g + 8) and two MMAs per set
-//     of eight activation rows; after the last slab of a tile the 16 warps' partial sums meet in
-//     shared memory and are added in warp order, so a row's value depends neither on M nor on the
-//     grid.
+//     lane loads its 16 bytes of x per (k-slab, 32-k step) straight from global memory, once -- at
+//     most 16 of them, 64 registers -- and x never touches shared memory, which is left to the
+//     ring (eight stages, 139 KB in flight per SM);
+//   * per stage and 32-k step a warp issues two 16-byte loads (the tile's rows g and g + 8) and two
+//     MMAs; after the last slab of a tile the 16 / NT warps that share a set add their 16 x 8
+//     partial sums through shared memory in a fixed order, so a row's value depends neither on M
+//     nor on the grid.  (Splitting only k over the warps, every warp carrying all sets, needed a
+//     16 x 8 NT partial per warp: at 32 rows the exchange cost 6 us of a 23 us launch.)
 // Every wait is bounded.
 #pragma once
 #include "common.cuh"
@@ -47,7 +49,8 @@ constexpr int MAX_FRAGS = 16;                 // (k-slabs) x (sets of 8 activati
 template <int NT>
 struct Cfg {
     static constexpr int MP = 8 * NT;                     // activation rows covered (zero rows past M)
-    static constexpr int RED_STRIDE = 16 * (MP + 1);      // floats of one warp's partial tile
+    static constexpr int KP = WARPS / NT;                 // warps that share a set: k parts of a stage
+    static constexpr int RED_STRIDE = 16 * 9;             // floats of one warp's 16 x 8 partial, padded rows
     static constexpr int RED_BYTES = WARPS * RED_STRIDE * 4;
 };
 
@@ -110,18 +113,20 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
         try_refill();  // the cache is immutable: its first slabs travel before the dependency wait
     }
     pdl_wait_prior();  // x (and y) belong to the predecessor until here
-    // this lane's B fragments: 16 bytes of activation row 8j + g at k = 512 s + 32 warp + 8 t
+    // this lane's B fragments: 16 bytes of activation row 8 (warp % NT) + g at
+    // k = 512 s + 32 (NT (warp / NT) + i) + 8 t for the NT steps i of the warp's k part
+    const uint32_t set = warp % (uint32_t)NT, kpart = warp / (uint32_t)NT;
     uint4 xf[SLABS][NT];
     {
-        const uint32_t g = lane >> 2, t = lane & 3u;
+        const uint32_t g = lane >> 2, t = lane & 3u, m = 8u * set + g;
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const uint32_t m = 8u * j + g, k = (uint32_t)s * KS + warp * 32u + t * 8u;
-                xf[s][j] = make_uint4(0u, 0u, 0u, 0u);
+            for (int i = 0; i < NT; ++i) {
+                const uint32_t k = (uint32_t)s * KS + (kpart * NT + i) * 32u + t * 8u;
+                xf[s][i] = make_uint4(0u, 0u, 0u, 0u);
                 if (warp < WARPS && m < M && k < K)  // K is a multiple of 8: whole pieces
-                    xf[s][j] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + k));
+                    xf[s][i] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + k));
             }
     }
     __syncthreads();  // barriers initialised before anyone waits on them
@@ -138,13 +143,11 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
     }
     if (warp < WARPS) {
         const uint32_t g = lane >> 2, t = lane & 3u;
-        const uint32_t a_lane = g * (uint32_t)PITCH + warp * 64u + t * 16u;  // row g of a stage; + 8 rows for g + 8
+        const uint32_t a_lane = g * (uint32_t)PITCH + kpart * (NT * 64u) + t * 16u;  // row g, first step of the k part
         bool ok = true;
         uint32_t stage = 0, parity = 0;
         for (uint32_t ti = 0; ti < my_tiles; ++ti) {
-            float acc[NT][4];
-#pragma unroll
-            for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int s = 0; s < SLABS; ++s) {
                 if (ok) {
@@ -153,34 +156,33 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
                 }
                 if (ok) {
                     const uint32_t st = ring + stage * (uint32_t)STAGE_BYTES + a_lane;
-                    const uint4 q0 = gemvtma::lds128(st);
-                    const uint4 q1 = gemvtma::lds128(st + 8u * (uint32_t)PITCH);
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        mma_bf16(acc[j], q0.x, q1.x, q0.y, q1.y, xf[s][j].x, xf[s][j].y);
-                        mma_bf16(acc[j], q0.z, q1.z, q0.w, q1.w, xf[s][j].z, xf[s][j].w);
+                    for (int i = 0; i < NT; ++i) {
+                        const uint4 q0 = gemvtma::lds128(st + (uint32_t)i * 64u);
+                        const uint4 q1 = gemvtma::lds128(st + (uint32_t)i * 64u + 8u * (uint32_t)PITCH);
+                        mma_bf16(acc, q0.x, q1.x, q0.y, q1.y, xf[s][i].x, xf[s][i].y);
+                        mma_bf16(acc, q0.z, q1.z, q0.w, q1.w, xf[s][i].z, xf[s][i].w);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_addr(&empty_bars[stage]));  // stage consumed
                 }
                 if (++stage == nstage) { stage = 0; parity ^= 1u; }
             }
-            // the 16 warps' partial tiles meet; thread (m, r) adds them in warp order
-            float* mine = red + (size_t)warp * C::RED_STRIDE;
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                mine[g * (C::MP + 1) + 8 * j + 2 * t] = acc[j][0];
-                mine[g * (C::MP + 1) + 8 * j + 2 * t + 1] = acc[j][1];
-                mine[(g + 8) * (C::MP + 1) + 8 * j + 2 * t] = acc[j][2];
-                mine[(g + 8) * (C::MP + 1) + 8 * j + 2 * t + 1] = acc[j][3];
-            }
+            // the KP warps of a set meet: partial [kpart][set] is 16 rows x 8 columns; thread (m, r) adds
+            // the KP partials of its output in k order
+            float* mine = red + (size_t)(kpart * NT + set) * C::RED_STRIDE;
+            mine[g * 9 + 2 * t] = acc[0];
+            mine[g * 9 + 2 * t + 1] = acc[1];
+            mine[(g + 8) * 9 + 2 * t] = acc[2];
+            mine[(g + 8) * 9 + 2 * t + 1] = acc[3];
             asm volatile("bar.sync 1, 512;" ::: "memory");
             const uint32_t row0 = (blockIdx.x + ti * gridDim.x) * 16u;
             for (uint32_t o = threadIdx.x; o < 16u * C::MP; o += WARPS * 32) {
                 const uint32_t m = o >> 4, r = o & 15u;
-                float v = red[r * (C::MP + 1) + m];
+                const float* src = red + (size_t)(m >> 3) * C::RED_STRIDE + r * 9u + (m & 7u);
+                float v = src[0];
 #pragma unroll
-                for (int w = 1; w < WARPS; ++w) v += red[(size_t)w * C::RED_STRIDE + r * (C::MP + 1) + m];
+                for (int p = 1; p < C::KP; ++p) v += src[(size_t)p * NT * C::RED_STRIDE];
                 if (m < M && row0 + r < N && ok) {
                     if (OUT_BF16) static_cast<uint16_t*>(y)[(size_t)m * N + row0 + r] = (uint16_t)float_to_bf16_bits(v);
                     else static_cast<float*>(y)[(size_t)m * N + row0 + r] = v;

@@ -128,9 +128,9 @@ MIORI_API int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, u
 // Where miori_linear4 sends a projection: 0 = packed-weight GEMV, 1 = narrow-batch kernel on the
 // bf16 cache, 2 = tcgen05 GEMM on the bf16 cache.  Measured on B200 in chains of dependent
 // launches (us per launch, 2048 -> 3072 / 2048 -> 2048 / 8192 -> 2048 / 2048 -> 16384):
-//   M = 8:  packed 4.4 / 3.9 / 9.0 / 10.6, narrow 4.1 / 3.2 / 7.7 / 11.8
-//   M = 16: packed 5.4 / 4.7 / 82 / 12.6,  narrow 4.8 / 3.6 / -- / 13.4,  GEMM 8.9 / 7.6 / 12.5 / 15.9
-//   M = 32: packed 10.8 / 7.2 / 162 / 32,  narrow 7.5 / 5.3 / -- / 20.1,  GEMM 8.6 / 7.8 / 12.9 / 15.9
+//   M = 8:  packed 4.4 / 3.9 / 8.9 / 10.6, narrow 4.1 / 3.2 / 7.4 / 11.7
+//   M = 16: packed 5.3 / 4.7 / 82 / 12.6,  narrow 4.4 / 3.4 / -- / 12.3,  GEMM 8.9 / 7.6 / 12.6 / 15.8
+//   M = 32: packed 10.8 / 7.1 / 162 / 32,  narrow 5.7 / 4.4 / -- / 17.5,  GEMM 8.6 / 7.8 / 12.8 / 16.0
 // Up to four rows stay on the packed weights with fp32 dequantization, as in the reference
 // (src/batch.cpp:223-230 cuts over to the cache above four rows).  Above that the cache is used
 // when given: by the narrow-batch kernel while the projection is short (at most two 16-row tiles
