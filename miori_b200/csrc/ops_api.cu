@@ -39,11 +39,12 @@ int gemv_entry(const char* op, const void* q, const void* s, const void* b, cons
     // every M).  By default it takes the 8-bit weights from three activation rows up: there the
     // mma.sync kernel needs a second column set (M = 3, 4) or does not apply at all (M > 4 would
     // fall to the multi-pass scalar kernel), and any batch wider than four rows when the caller
-    // asks for fp32 dequantization (MIORI_GEMV_EXACT), and long streams of 4-bit weights (four
-    // 128-row tiles per SM and more, up to four activation rows), where it runs two CTAs per SM
-    // and measured 14-17 % faster.  Elsewhere the mma.sync kernel with its shorter
+    // asks for fp32 dequantization (MIORI_GEMV_EXACT), and long streams of 4-bit weights in groups
+    // of 64 (four 128-row tiles per SM and more, up to four activation rows), where it runs two
+    // CTAs per SM and measured 14-17 % faster (at group 32 it drains twice the accumulator columns
+    // and measured 7-30 % slower, so those stay on the mma.sync kernel).  Elsewhere the mma.sync kernel with its shorter
     // pipeline measured faster and stays the default; MIORI_TUNE_GEMV_UMMA forces this one.
-    const bool long_stream4 = BITS == 4 && M <= 4 && (N + 127u) / 128u >= 4u * (uint32_t)sm_count();
+    const bool long_stream4 = BITS == 4 && M <= 4 && group == 64 && (N + 127u) / 128u >= 4u * (uint32_t)sm_count();
     const bool umma_default = (BITS == 8 && M >= 3) || (force_exact && M > 4) || long_stream4;
     if (!force_simt && !no_bulk && !(flags & MIORI_TUNE_GEMV_MMASYNC) &&
         (umma_default || (flags & MIORI_TUNE_GEMV_UMMA))) {
