@@ -210,9 +210,9 @@ int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, uint32_t M,
 /* y[M][N] (fp32) = x[M][K] (bf16) x W^T.  Up to four rows stream the packed 4-bit weights with
  * fp32 dequantization (miori_gemv4), the reference's own cut-over.  Wider batches multiply the bf16
  * cache when `cache` is given -- with the narrow-batch kernel (miori_gemv_bf16_cache) while the
- * projection is short, with the tensor-core GEMM (miori_gemm_bf16_cache_ws) for long rows or wide
- * outputs at more than 16 rows -- and otherwise stay on the packed weights (as does everything
- * when no cache is given, M <= 32).  miori_linear4_route tells which: 0 packed GEMV, 1 narrow-batch
+ * projection is short and for 9..16 rows, with the tensor-core GEMM (miori_gemm_bf16_cache_ws) for
+ * long rows or wide outputs at more than 16 rows -- and otherwise stay on the packed weights (wide
+ * outputs up to 8 rows, and everything when no cache is given, M <= 32).  miori_linear4_route tells which: 0 packed GEMV, 1 narrow-batch
  * cache kernel, 2 tensor-core GEMM (host-only; for logs and tests). */
 int miori_linear4_route(uint32_t M, uint32_t N, uint32_t K, int has_cache);
 int miori_linear4(const void* q, const void* s, const void* b, const void* cache, const void* x,

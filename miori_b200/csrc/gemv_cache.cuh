@@ -147,7 +147,9 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
         bool ok = true;
         uint32_t stage = 0, parity = 0;
         for (uint32_t ti = 0; ti < my_tiles; ++ti) {
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // two accumulation chains (even and odd steps), so that consecutive MMAs do not wait for
+            // one another; they meet in a fixed order before the exchange
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int s = 0; s < SLABS; ++s) {
                 if (ok) {
@@ -161,7 +163,7 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
                         const uint4 q0 = gemvtma::lds128(st + (uint32_t)i * 64u);
                         const uint4 q1 = gemvtma::lds128(st + (uint32_t)i * 64u + 8u * (uint32_t)PITCH);
                         mma_bf16(acc, q0.x, q1.x, q0.y, q1.y, xf[s][i].x, xf[s][i].y);
-                        mma_bf16(acc, q0.z, q1.z, q0.w, q1.w, xf[s][i].z, xf[s][i].w);
+                        mma_bf16(acc2, q0.z, q1.z, q0.w, q1.w, xf[s][i].z, xf[s][i].w);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_addr(&empty_bars[stage]));  // stage consumed
@@ -171,6 +173,8 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
             // the KP warps of a set meet: partial [kpart][set] is 16 rows x 8 columns; thread (m, r) adds
             // the KP partials of its output in k order
             float* mine = red + (size_t)(kpart * NT + set) * C::RED_STRIDE;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] += acc2[e];
             mine[g * 9 + 2 * t] = acc[0];
             mine[g * 9 + 2 * t + 1] = acc[1];
             mine[(g + 8) * 9 + 2 * t] = acc[2];

@@ -129,23 +129,23 @@ MIORI_API int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, u
 // Where miori_linear4 sends a projection: 0 = packed-weight GEMV, 1 = narrow-batch kernel on the
 // bf16 cache, 2 = tcgen05 GEMM on the bf16 cache.  Measured on B200 in chains of dependent
 // launches (us per launch, 2048 -> 3072 / 2048 -> 2048 / 8192 -> 2048 / 2048 -> 16384):
-//   M = 8:  packed 4.4 / 3.9 / 8.9 / 10.6, narrow 4.1 / 3.2 / 7.4 / 11.7
-//   M = 16: packed 5.3 / 4.7 / 82 / 12.6,  narrow 4.4 / 3.4 / -- / 12.3,  GEMM 8.9 / 7.6 / 12.6 / 15.8
-//   M = 32: packed 10.8 / 7.1 / 162 / 32,  narrow 5.7 / 4.4 / -- / 17.5,  GEMM 8.6 / 7.8 / 12.8 / 16.0
+//   M = 8:  packed 4.4 / 3.9 / 8.9 / 10.5, narrow 4.1 / 3.2 / 7.6 / 11.8
+//   M = 16: packed 5.3 / 4.7 / 82 / 12.6,  narrow 4.3 / 3.3 / -- / 11.9,  GEMM 8.9 / 7.6 / 12.6 / 15.7
+//   M = 32: packed 10.8 / 7.1 / 162 / 32,  narrow 5.6 / 4.3 / -- / 17.0,  GEMM 8.6 / 7.8 / 12.8 / 15.8
 // Up to four rows stay on the packed weights with fp32 dequantization, as in the reference
 // (src/batch.cpp:223-230 cuts over to the cache above four rows).  Above that the cache is used
 // when given: by the narrow-batch kernel while the projection is short (at most two 16-row tiles
 // per SM: its launch is cheap, but it streams four times the bytes and its mma.sync rate caps it
-// on long streams), else by the packed GEMV while that still has a fast form (up to 16 rows of
-// K <= 2048), else by the tensor-core GEMM.
+// on long streams) and for 9..16 rows of any width, else by the packed GEMV up to 8 rows, else by
+// the tensor-core GEMM.
 static int linear4_route(uint32_t M, uint32_t N, uint32_t K, bool has_cache) {
     if (M <= 4 || !has_cache) return 0;
     const uint32_t tiles = (N + 15u) / 16u, slabs = (K + 511u) / 512u;
     const uint32_t frags = (slabs <= 1 ? 1u : slabs <= 2 ? 2u : slabs <= 4 ? 4u : slabs <= 8 ? 8u : 16u) *
                            (M <= 8 ? 1u : M <= 16 ? 2u : 4u);
-    if (tiles <= 2u * (uint32_t)sm_count() && slabs <= 16u && frags <= (uint32_t)gemvcache::MAX_FRAGS && K % 8 == 0)
-        return 1;
-    if (M <= 8 || (M <= 16 && K <= 2048)) return 0;
+    const bool fits = slabs <= 16u && frags <= (uint32_t)gemvcache::MAX_FRAGS && K % 8 == 0;
+    if (fits && (tiles <= 2u * (uint32_t)sm_count() || (M > 8 && M <= 16))) return 1;
+    if (M <= 8) return 0;
     return 2;
 }
 

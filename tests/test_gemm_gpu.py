@@ -145,7 +145,7 @@ def test_linear_dispatch(port, M, N, K):
     assert_close(y_nocache.cpu().numpy(), want, what=f"linear4 (no cache) M={M}")
     r = miori_b200.lib.miori_linear4_route(M, N, K, 1)
     assert miori_b200.lib.miori_linear4_route(M, N, K, 0) == 0
-    assert (r == 0) == (M <= 4 or (N == 6144 and (M <= 8 or M <= 16)))
+    assert (r == 0) == (M <= 4 or (N == 6144 and M <= 8))
     if r == 0:
         assert torch.equal(y, miori_b200.gemv4(q, s, b, x, group=64))
     elif r == 1:
