@@ -649,14 +649,27 @@ def main():
         d2h += sum(t.numel() * 4 for t in dev_y[M])
         h2d += host_x[M].numel() * 2
 
+    # a pass's results travel back on a second stream while the next pass runs: the host waits for
+    # pass i only after it has enqueued pass i + 1 (what a decode loop with two batches in flight does)
+    back = torch.cuda.Stream(device=dev)
+    computed = {M: torch.cuda.Event() for M in M_SWEEP}
+    landed = {M: torch.cuda.Event() for M in M_SWEEP}
+
     def e2e_step():
+        prev = None
         for M in M_SWEEP:
             check(lib.miori_memcpy_h2d(x_flat[M].data_ptr(), host_x[M].data_ptr(),
                                        host_x[M].numel() * 2, stream))
             graphs[M].replay()
+            computed[M].record()
+            back.wait_event(computed[M])
             for hy, dy in zip(host_y[M], dev_y[M]):
-                check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, stream))
-            check(lib.miori_stream_sync(stream))  # the host consumes this pass's result
+                check(lib.miori_memcpy_d2h(hy.data_ptr(), dy.data_ptr(), hy.numel() * 4, back.cuda_stream))
+            landed[M].record(back)
+            if prev is not None:
+                landed[prev].synchronize()  # the host consumes the previous pass's result
+            prev = M
+        landed[prev].synchronize()
 
     say("per-M breakdown done")
     e2e_step()
