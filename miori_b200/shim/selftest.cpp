@@ -6,6 +6,7 @@
 
 #include <cstring>
 #include <exception>
+#include <initializer_list>
 #include <stdexcept>
 #include <string>
 
@@ -125,6 +126,54 @@ extern "C" __attribute__((visibility("default"))) int miori_shim_test_naive(
         bA->release();
         bB->release();
         bC->release();
+        return 0;
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return -1;
+    }
+}
+
+// The neighbours of a projection through the operator API, one decode step's worth: embed8 picks
+// token rows out of the 8-bit table (bf16 [T][K]), rmsnorm normalises an fp32 row block against a
+// bf16 weight vector, silu_mul gates (reference src/ops.h:16-24, 35-37).
+extern "C" __attribute__((visibility("default"))) int miori_shim_test_neighbors(
+    const uint32_t* q8, const uint16_t* s8, const uint16_t* b8, uint32_t rows8, const int32_t* tokens,
+    uint32_t T, uint16_t* emb_out, const float* x, const uint16_t* gamma, uint16_t* norm_out,
+    uint32_t rows, uint32_t K, float eps, const float* gate, const float* up, uint16_t* act_out, uint32_t n_act) {
+    using namespace miori;
+    try {
+        Metal m;
+        std::string err;
+        if (!m.init("", err)) throw std::runtime_error(err);
+        Weights w;
+        const size_t qb = (size_t)rows8 * K, sb = (size_t)rows8 * (K / kGroup) * 2;
+        if (!w.reserve(m, qb + 2 * sb + (size_t)K * 2 + 2048, err)) throw std::runtime_error(err);
+        const Tensor& tq = w.add("e.weight", "U32", {(int64_t)rows8, (int64_t)(K / 4)}, q8, qb);
+        const Tensor& ts = w.add("e.scales", "BF16", {(int64_t)rows8, (int64_t)(K / kGroup)}, s8, sb);
+        const Tensor& tb = w.add("e.biases", "BF16", {(int64_t)rows8, (int64_t)(K / kGroup)}, b8, sb);
+        const Tensor& tg = w.add("n.weight", "BF16", {(int64_t)K}, gamma, (size_t)K * 2);
+        MTL::Buffer* btok = m.new_buffer((size_t)T * 4);
+        MTL::Buffer* bemb = m.new_buffer((size_t)T * K * 2);
+        MTL::Buffer* bx = m.new_buffer((size_t)rows * K * 4);
+        MTL::Buffer* bn = m.new_buffer((size_t)rows * K * 2);
+        MTL::Buffer* bg = m.new_buffer((size_t)n_act * 4);
+        MTL::Buffer* bu = m.new_buffer((size_t)n_act * 4);
+        MTL::Buffer* ba = m.new_buffer((size_t)n_act * 2);
+        std::memcpy(btok->contents(), tokens, (size_t)T * 4);
+        std::memcpy(bx->contents(), x, (size_t)rows * K * 4);
+        std::memcpy(bg->contents(), gate, (size_t)n_act * 4);
+        std::memcpy(bu->contents(), up, (size_t)n_act * 4);
+        auto* cb = m.begin();
+        auto* e = cb->computeCommandEncoder();
+        embed8(m, e, w, tq, ts, tb, btok, bemb, T, K);
+        rmsnorm(m, e, bx, w, tg, bn, rows, K, eps);
+        silu_mul(m, e, bg, bu, ba, n_act);
+        e->endEncoding();
+        m.submit(cb, true);
+        std::memcpy(emb_out, bemb->contents(), (size_t)T * K * 2);
+        std::memcpy(norm_out, bn->contents(), (size_t)rows * K * 2);
+        std::memcpy(act_out, ba->contents(), (size_t)n_act * 2);
+        for (MTL::Buffer* b : {btok, bemb, bx, bn, bg, bu, ba}) b->release();
         return 0;
     } catch (const std::exception& ex) {
         g_err = ex.what();

@@ -90,3 +90,31 @@ def test_strided_gemm_and_peer_entries_reject_bad_arguments():
     assert lib.miori_allgather(None, ok, 0, 1, 16, 0, 16, 4, 0, None) == -1
     assert lib.miori_peers_status(None) == -1
     assert lib.miori_peers_destroy(None) == 0
+
+
+def test_neighbor_and_narrow_batch_entries_reject_bad_arguments():
+    ok = 0x1000  # aligned, never dereferenced: validation fails first
+    assert lib.miori_gemv_bf16_cache(None, ok, ok, 8, 64, 64, 0, None) == -1
+    assert b"null" in lib.miori_last_error()
+    assert lib.miori_gemv_bf16_cache(ok, ok, ok, 0, 64, 64, 0, None) == -1
+    assert lib.miori_gemv_bf16_cache(ok, ok, ok, 33, 64, 64, 0, None) == -1
+    assert b"1..32" in lib.miori_last_error()
+    assert lib.miori_gemv_bf16_cache(ok, ok, ok, 8, 64, 100, 0, None) == -1
+    assert b"multiple of 8" in lib.miori_last_error()
+    assert lib.miori_gemv_bf16_cache(ok, ok + 2, ok, 8, 64, 64, 0, None) == -1
+    assert b"aligned" in lib.miori_last_error()
+    # more activations than the kernel keeps in registers: refused on the host, nothing launched
+    assert lib.miori_gemv_bf16_cache(ok, ok, ok, 32, 64, 8192, 0, None) == -1
+    assert b"registers" in lib.miori_last_error()
+    assert lib.miori_rmsnorm(None, ok, ok, 1, 64, 1e-5, 0, None) == -1
+    assert lib.miori_rmsnorm(ok, ok, ok, 0, 64, 1e-5, 0, None) == -1
+    assert lib.miori_argmax(ok, 0, 0, ok, ok, None) == -1
+    assert lib.miori_argmax(None, 8, 0, ok, ok, None) == -1
+    # the routing query is pure host arithmetic
+    assert lib.miori_linear4_route(4, 2048, 2048, 1) == 0      # up to four rows: packed weights
+    assert lib.miori_linear4_route(8, 2048, 2048, 0) == 0      # no cache: packed weights
+    assert lib.miori_linear4_route(8, 2048, 2048, 1) == 1      # short projection: narrow-batch cache kernel
+    assert lib.miori_linear4_route(8, 16384, 2048, 1) == 0     # wide projection, few rows: packed weights
+    assert lib.miori_linear4_route(16, 16384, 2048, 1) == 1
+    assert lib.miori_linear4_route(32, 16384, 2048, 1) == 2    # wide and more than 16 rows: tensor-core GEMM
+    assert lib.miori_linear4_route(32, 2048, 8192, 1) == 2     # K too long for the registers

@@ -87,3 +87,33 @@ def test_errors_surface_as_messages(shim):
     rc = shim.miori_shim_test_gemv(4, z.ctypes.data, z.ctypes.data, z.ctypes.data, z.ctypes.data,
                                    y.ctypes.data, 16, 48, 1)
     assert rc != 0 and b"multiple" in shim.miori_shim_last_error()
+
+
+def test_neighbors_through_operator_api(shim, port):
+    """embed8, rmsnorm and silu_mul with the reference's signatures (src/ops.h:16-24, 35-37), one
+    command buffer, against the oracle's restatements of the shaders: the embedding bit for bit,
+    the two float ops within one bf16 ulp."""
+    rows8, K, T, rows, n_act = 300, 2048, 5, 3, 4096
+    q, s, b = synth.make_weight(rows8, K, 8, 32, seed=41)
+    tokens = np.array([0, 299, 7, 7, 123], np.int32)
+    g = np.random.default_rng(3)
+    x = g.standard_normal((rows, K)).astype(np.float32) * 3.0
+    gamma = u16(synth.make_activation(1, K, seed=5)).reshape(-1)
+    gate = g.standard_normal(n_act).astype(np.float32) * 4.0
+    up = g.standard_normal(n_act).astype(np.float32)
+    qn, sn, bn = u32(q), u16(s), u16(b)
+    emb = np.zeros((T, K), np.uint16)
+    norm = np.zeros((rows, K), np.uint16)
+    act = np.zeros(n_act, np.uint16)
+    p, u, f = C.c_void_p, C.c_uint32, C.c_float
+    shim.miori_shim_test_neighbors.argtypes = [p, p, p, u, p, u, p, p, p, p, u, u, f, p, p, p, u]
+    rc = shim.miori_shim_test_neighbors(qn.ctypes.data, sn.ctypes.data, bn.ctypes.data, rows8, tokens.ctypes.data, T,
+                                        emb.ctypes.data, x.ctypes.data, gamma.ctypes.data, norm.ctypes.data, rows, K,
+                                        1e-5, gate.ctypes.data, up.ctypes.data, act.ctypes.data, n_act)
+    assert rc == 0, shim.miori_shim_last_error()
+    assert np.array_equal(emb, port.embed8(qn, sn, bn, tokens, 32))
+
+    def ulps(a, w):  # distance in bf16 steps between two arrays of bf16 bit patterns of equal sign
+        return np.abs(a.astype(np.int32) - w.astype(np.int32)).max()
+    assert ulps(norm, port.rmsnorm(x, gamma, 1e-5)) <= 1
+    assert ulps(act, port.silu_mul(gate, up)) <= 1
