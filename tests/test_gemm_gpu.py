@@ -177,6 +177,25 @@ def test_narrow_batch_cache_kernel(port, M, N, K):
     assert miori_b200.lib.miori_device_error_poll() == 0
 
 
+def test_narrow_batch_cache_kernel_random_shapes():
+    """Sixty seeded random shapes -- N from 1 (ragged tiles, fewer tiles than SMs) to a few thousand,
+    K any multiple of 8 within the kernel's range (ragged last slab, K shorter than one MMA step's
+    32), every batch class -- against a plain fp32 product of the same bf16 operands."""
+    g = torch.Generator().manual_seed(1234)
+    for case in range(60):
+        M = int(torch.randint(1, 33, (1,), generator=g))
+        kmax = 8192 if M <= 8 else 4096 if M <= 16 else 2048
+        K = 8 * int(torch.randint(1, kmax // 8 + 1, (1,), generator=g))
+        N = int(torch.randint(1, 3000, (1,), generator=g)) if case % 3 else int(torch.randint(1, 40, (1,), generator=g))
+        W = (torch.randn((N, K), generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        x = torch.randn((M, K), generator=g).to(torch.bfloat16).to(DEV)
+        y = miori_b200.gemv_bf16_cache(x, W.reshape(-1), N)
+        want = x.float() @ W.float().T
+        err = float((y - want).abs().max() / want.abs().max().clamp_min(1e-30))
+        assert err <= 1e-4, f"case {case}: M={M} N={N} K={K} rel={err:.2e}"
+    assert miori_b200.lib.miori_device_error_poll() == 0
+
+
 def test_narrow_batch_cache_kernel_refuses_what_it_cannot_hold():
     _, _, _, cache = _weights(64, 8192, 64, seed=3)
     x = synth.make_activation(16, 8192, seed=4, device=DEV)
