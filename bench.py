@@ -748,9 +748,10 @@ def main():
 
 def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world, grp):
     """The 8-bit head (N=131072, K=2048, M=1, bf16 logits) with its rows split over the ranks.
-    Two ways to finish: the logits gathered on every rank by the GEMV's own epilogue, or -- for greedy
-    sampling -- only each rank's best (value, index) exchanged (two 8-byte packets per rank).  Every
-    rank cycles through a pool of distinct shards larger than L2; GB/s counts the whole matrix."""
+    Three ways to finish: the logits gathered on every rank by the GEMV's own epilogue; or -- for
+    greedy sampling -- only each rank's best (value, index) exchanged (two 8-byte packets per rank),
+    by a second kernel after the GEMV or by the GEMV's own epilogue.  Every rank cycles through a
+    pool of distinct shards larger than L2; GB/s counts the whole matrix."""
     import torch.distributed as dist
     N, K = 131072, 2048
     rows = N // world
@@ -766,6 +767,7 @@ def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world,
     x = synth.make_activation(1, K, seed=9, device=dev)
     off = grp.alloc(N * 2)
     off_best = grp.alloc(256)
+    off_own, off_pick = grp.alloc(N * 2), grp.alloc(256)
     y_local = torch.empty((1, rows), dtype=torch.bfloat16, device=dev)
     flags = miori_b200.LAUNCH_PDL | miori_b200.OUT_BF16
     by = packed_bytes(N, K, 8, G)
@@ -779,8 +781,13 @@ def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world,
             miori_b200.gemv8(q, sc, bi, x, group=G, flags=flags, out=y_local)
             grp.argmax_allreduce(y_local.view(-1), rank * rows, off_best, flags=miori_b200.LAUNCH_PDL)
 
+    def run_fused():
+        for q, sc, bi in pool:
+            grp.gemv_argmax(8, q, sc, bi, x, off_own, off_pick, rank * rows, N, group=G, flags=flags)
+
     out = {"n_gpus": world, "rows_per_gpu": rows, "pool": npool, "out": "bf16"}
-    for name, run in (("gather_logits", run_gather), ("exchange_argmax", run_argmax)):
+    for name, run in (("gather_logits", run_gather), ("exchange_argmax", run_argmax),
+                      ("argmax_in_the_gemv_epilogue", run_fused)):
         run()
         torch.cuda.synchronize()
         dist.barrier()
@@ -797,11 +804,13 @@ def config1_sharded(torch, miori_b200, synth, dev, G, peaks, timed, rank, world,
     logits = grp.tensor(off, (N,), torch.bfloat16).float()
     want = int(torch.argmax((logits == logits.max()).to(torch.int8)).item())
     got_i, got_v = grp.argmax_result(off_best)
-    out["argmax_matches_gathered_logits"] = bool(got_i == want and got_v == float(logits.max()))
+    out["argmax_matches_gathered_logits"] = bool(got_i == want and got_v == float(logits.max()) and
+                                                 grp.gemv_argmax_result(off_pick) == (got_i, got_v))
     out["us"], out["gbs"], out["frac_of_hbm_peak"] = (out["gather_logits"][k] for k in ("us", "gbs", "frac_of_hbm_peak"))
     out["how"] = ("CUDA graph of dependent launches over a pool of distinct shards (> L2 per rank); "
-                  "gather_logits ends with the whole logits vector on every rank, exchange_argmax with "
-                  "the winning (value, index) pair on every rank")
+                  "gather_logits ends with the whole logits vector on every rank, exchange_argmax (GEMV, then "
+                  "a second kernel) and argmax_in_the_gemv_epilogue (one launch) with the winning (value, index) "
+                  "pair on every rank")
     return out
 
 

@@ -277,6 +277,24 @@ int miori_allgather(miori_peers* g, const void* src, size_t y_offset, uint32_t M
  * Same launch-order contract as the *_allgather entries. */
 int miori_argmax_allreduce(miori_peers* g, const void* v, uint32_t n_local, uint32_t index0,
                            size_t y_offset, uint32_t flags, void* stream);
+/* The head of a greedy decode step in one launch: this rank's rows of y = W x (one activation row)
+ * go to y_offset of its own arena only, every thread keeps the best (value, index) of what it
+ * stores, and the CTA that finishes last exchanges the rank's best with the peers, so that when
+ * the kernel completes the winning token is on every rank and nothing but 16 bytes per peer has
+ * crossed NVLink.  At best_offset (16-byte aligned, miori_gemv_argmax_bytes(world) bytes, zero
+ * before the first use -- a fresh arena is) lie 16 bytes of scratch, then [rank][value, index]
+ * and the winner [value, index] as 32-bit words: the winner sits 16 + 8 * world bytes in.  With
+ * bf16 output the rounded logits are compared, so the result equals the arg-max of the gathered
+ * bf16 vector; ties go to the lowest index, NaN never wins.  A world of one rank works too (no
+ * exchange): the single-GPU form of "LM head, then pick".  Replaces the reference's gemv8 on the
+ * head followed by the host loop of src/engine.cpp:740-747. */
+size_t miori_gemv_argmax_bytes(int world);
+int miori_gemv4_argmax(miori_peers* g, const void* q, const void* s, const void* b, const void* x,
+                       size_t y_offset, size_t best_offset, uint32_t n_local, uint32_t row0,
+                       uint32_t n_total, uint32_t K, uint32_t group, uint32_t flags, void* stream);
+int miori_gemv8_argmax(miori_peers* g, const void* q, const void* s, const void* b, const void* x,
+                       size_t y_offset, size_t best_offset, uint32_t n_local, uint32_t row0,
+                       uint32_t n_total, uint32_t K, uint32_t group, uint32_t flags, void* stream);
 
 /* ---- the steps either side of a projection (reference src/engine.cpp:389-413, 484-502) and the
  *      8-bit embedding gather that shares its table with the LM head. -------------------------- */

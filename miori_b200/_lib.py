@@ -55,6 +55,9 @@ _SIGS = {
     "miori_gemv_bf16_cache": (_i, [_p, _p, _p, _u32, _u32, _u32, _u32, _p]),
     "miori_gemm_plan": (_i, [_u32, _u32, _u32, _sz, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
     "miori_linear4": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p, _sz, _p]),
+    "miori_gemv_argmax_bytes": (_sz, [_i]),
+    "miori_gemv4_argmax": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_gemv8_argmax": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _u32, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_peers_create": (_i, [_i, _i, _sz, C.POINTER(_p)]),
     "miori_peers_handle_bytes": (_sz, []),
     "miori_peers_handle": (_i, [_p, _p]),

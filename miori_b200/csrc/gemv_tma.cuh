@@ -268,7 +268,12 @@ __device__ __forceinline__ unsigned long long gtimer() {
 #define TMA_MARK(i) do { } while (0)
 #endif
 
-template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR>
+// ARGMAX (with SHARDED, one activation row): the head of a greedy decode step.  The rows go to this
+// rank's y only -- no packets -- and every thread tracks the best (value, index) of what it stores;
+// the candidates meet in a 64-bit atomic maximum, and the CTA that finishes last exchanges this
+// rank's best with the peers (peers.cuh: peer_argmax_exchange), so the kernel ends with the winning
+// token on every rank and nothing else has crossed NVLink.
+template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR, bool ARGMAX = false>
 __global__ void __launch_bounds__(THREADS, (NT == 1 && !ROOMY) ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_s,
@@ -276,7 +281,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const uint16_t* __restrict__ slin, const uint16_t* __restrict__ blin,
                 const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
                 uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar,
-                const PeerArgs pa, uint32_t n_total, uint32_t row0, size_t y_off) {
+                const PeerArgs pa, uint32_t n_total, uint32_t row0, size_t y_off,
+                unsigned long long* __restrict__ best) {
+    static_assert(!ARGMAX || SHARDED, "the arg-max epilogue lives in the sharded instantiation");
     using namespace gemvmma;
     const uint32_t nstage = ngrp * nsg;  // every active group owns a private ring of nsg stages
     constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
@@ -422,6 +429,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // template parameter rather than a run-time test because the single-GPU instantiation then
     // compiles exactly as if the peer path did not exist (a run-time branch cost 3-16 %).
     const uint32_t world = SHARDED ? pa.world : 0u;
+    unsigned long long my_best = 0ull;  // ARGMAX: key of the best element this thread has stored
     // one output element: y[m][row0 + row]
     auto store_out = [&](uint32_t m, uint32_t row, float v) {
         if (BITS == 8) v *= x_rescale[m];
@@ -429,7 +437,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t bits = OUT_BF16 ? float_to_bf16_bits(v) : __float_as_uint(v);
         if (OUT_BF16) reinterpret_cast<uint16_t*>(y)[idx] = (uint16_t)bits;
         else reinterpret_cast<uint32_t*>(y)[idx] = bits;
-        if constexpr (SHARDED) {
+        if constexpr (ARGMAX) {  // compare what was stored (the rounded value when the output is bf16)
+            if (v == v) {
+                const unsigned long long key = peer_best_key(OUT_BF16 ? bits << 16 : bits, row0 + row);
+                my_best = key > my_best ? key : my_best;
+            }
+        } else if constexpr (SHARDED) {
             if (world > 1u) {
                 const uint32_t e = peer_epoch(pa);
                 const size_t elem = y_off / (OUT_BF16 ? 2u : 4u) + idx;
@@ -759,7 +772,31 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
     }
-    if constexpr (SHARDED) {
+    if constexpr (ARGMAX) {  // every thread of the CTA gets here: no early exits above
+        unsigned long long k = my_best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, k, o);
+            k = other > k ? other : k;
+        }
+        __shared__ unsigned long long warp_keys[WARPS + 1];
+        if (lane == 0) warp_keys[warp] = k;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (uint32_t w = 1; w <= (uint32_t)WARPS; ++w) k = warp_keys[w] > k ? warp_keys[w] : k;
+            if (k != 0ull) atomicMax(best, k);  // one candidate per CTA
+            unsigned int* arrived = reinterpret_cast<unsigned int*>(best + 1);
+            __threadfence();
+            if (atomicAdd(arrived, 1u) == gridDim.x - 1u) {  // the last CTA: every candidate is in
+                __threadfence();
+                const unsigned long long win = atomicExch(best, 0ull);  // read, and reset for the next launch
+                *arrived = 0u;
+                uint32_t* pairs = reinterpret_cast<uint32_t*>(best) + 4;
+                const size_t base = (size_t)(reinterpret_cast<uint8_t*>(pairs) - (pa.local + PEER_CTL_BYTES)) / 4u;
+                peer_argmax_exchange(pa, pairs, base, peer_best_from_key(win));
+            }
+        }
+    } else if constexpr (SHARDED) {
         if (world > 1u) {  // every thread of the CTA gets here: no early exits above
             const uint32_t e = peer_epoch(pa);
             __syncthreads();
@@ -789,6 +826,9 @@ struct Shard {
     PeerArgs pa = {};
     uint32_t n_total = 0, row0 = 0;
     size_t y_off = 0;
+    // arg-max epilogue (one activation row): 16 bytes of zeroed scratch {key, arrivals} followed by
+    // the (2 world + 2) words of the candidates and the winner, inside the local arena; null: off
+    unsigned long long* best = nullptr;
 };
 
 // Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
@@ -864,11 +904,11 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
                       CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     const uint8_t* ql = linear ? reinterpret_cast<const uint8_t*>(q) : nullptr;
-    cudaError_t e;
-#define MIORI_TMA_LAUNCH(OB, SH)                                                                 \
+    cudaError_t e = cudaSuccess;
+#define MIORI_TMA_LAUNCH(OB, SH, AM)                                                             \
     do {                                                                                         \
-        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR>              \
-                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR>;               \
+        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM>          \
+                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM>;           \
         e = cudaSuccess;                                                                         \
         if (smem_l > 48 * 1024)                                                                  \
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_l); \
@@ -876,15 +916,27 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
             e = launch(kern, dim3(grid), dim3(THREADS), smem_l, stream, pdl, tq, ts, tb, ql,     \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
                        reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
-                       sh.pa, sh.pa.world > 1 ? sh.n_total : N, sh.pa.world > 1 ? sh.row0 : 0u, sh.y_off); \
+                       sh.pa, placed ? sh.n_total : N, placed ? sh.row0 : 0u, sh.y_off, sh.best);  \
     } while (0)
     const bool sharded = sh.pa.world > 1;
+    constexpr bool can_argmax = EXACT && NT == 1 && !PAIR;  // the one- and two-row kernels
+    const bool argmax = sh.best != nullptr;
+    if (argmax && (!can_argmax || M != 1))
+        return fail(MIORI_E_INVALID, "the arg-max epilogue takes one activation row");
+    const bool placed = sharded || argmax;  // y is a slice of an n_total-row output
     const bool roomy = NT == 1 && plan.roomy;
     const size_t smem_l = plan.pad ? std::max<size_t>(smem, 120 * 1024) : smem;
-    if (flags & MIORI_OUT_BF16) {
-        if (sharded) MIORI_TMA_LAUNCH(true, true); else MIORI_TMA_LAUNCH(true, false);
-    } else {
-        if (sharded) MIORI_TMA_LAUNCH(false, true); else MIORI_TMA_LAUNCH(false, false);
+    if constexpr (can_argmax) {
+        if (argmax) {
+            if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true, true, true); else MIORI_TMA_LAUNCH(false, true, true);
+        }
+    }
+    if (!argmax) {
+        if (flags & MIORI_OUT_BF16) {
+            if (sharded) MIORI_TMA_LAUNCH(true, true, false); else MIORI_TMA_LAUNCH(true, false, false);
+        } else {
+            if (sharded) MIORI_TMA_LAUNCH(false, true, false); else MIORI_TMA_LAUNCH(false, false, false);
+        }
     }
 #undef MIORI_TMA_LAUNCH
     if (e != cudaSuccess) return cuda_fail(e, "gemv_tma launch");

@@ -70,38 +70,8 @@ argmax_allreduce_kernel(const PeerArgs pa, const void* __restrict__ v, uint32_t 
     pdl_wait_prior();
     const neighbors::Best mine = neighbors::cluster_argmax<BF16>(v, n_local, index0, warp_best, cta_best);
     if (neighbors::cluster_ctarank() == 0u && threadIdx.x == 0) {
-        uint32_t* y = reinterpret_cast<uint32_t*>(pa.local + PEER_CTL_BYTES + y_off);
-        const size_t base = y_off / 4u;
-        const uint32_t world = pa.world > 1u ? pa.world : 1u, rank = pa.world > 1u ? pa.rank : 0u;
-        y[2u * rank] = __float_as_uint(mine.v);
-        y[2u * rank + 1u] = mine.i;
-        neighbors::Best all = mine;
-        if (pa.world > 1u) {
-            const uint32_t e = peer_epoch(pa);
-            for (uint32_t p = 0; p < world; ++p) {
-                if (p == rank) continue;
-                uint8_t* arena = peer_arena(pa, p);
-                peer_send(peer_slot(pa, arena, e, base + 2u * rank), __float_as_uint(mine.v), e);
-                peer_send(peer_slot(pa, arena, e, base + 2u * rank + 1u), mine.i, e);
-            }
-            bool ok = true;
-            all = neighbors::Best{-INFINITY, 0xFFFFFFFFu};
-            for (uint32_t p = 0; p < world && ok; ++p) {
-                neighbors::Best b = mine;
-                if (p != rank) {
-                    uint32_t vb = 0, ib = 0;
-                    ok = peer_recv(pa, peer_slot(pa, pa.local, e, base + 2u * p), e, vb) &&
-                         peer_recv(pa, peer_slot(pa, pa.local, e, base + 2u * p + 1u), e, ib);
-                    b = neighbors::Best{__uint_as_float(vb), ib};
-                    y[2u * p] = vb;
-                    y[2u * p + 1u] = ib;
-                }
-                if (ok) all = neighbors::better(all, b);
-            }
-            peer_finish_single(pa, e);
-        }
-        y[2u * world] = __float_as_uint(all.v);
-        y[2u * world + 1u] = all.i;
+        uint32_t* pairs = reinterpret_cast<uint32_t*>(pa.local + PEER_CTL_BYTES + y_off);
+        peer_argmax_exchange(pa, pairs, y_off / 4u, PeerBest{mine.v, mine.i});
     }
 }
 
@@ -146,7 +116,7 @@ template <int BITS>
 static int gemv_allgather(const char* op, miori_peers* g, const void* q, const void* s, const void* b,
                           const void* x, size_t y_offset, uint32_t n_local, uint32_t row0,
                           uint32_t n_total, uint32_t K, uint32_t M, uint32_t group, uint32_t flags,
-                          void* stream) {
+                          void* stream, const size_t* best_offset = nullptr) {
     int rc = check_peers(op, g);
     if (rc) return rc;
     if (!q || !s || !b || !x) return fail(MIORI_E_INVALID, "%s: null pointer", op);
@@ -171,6 +141,13 @@ static int gemv_allgather(const char* op, miori_peers* g, const void* q, const v
         sh.pa.world = 0;
         if (row0 != 0 || n_local != n_total)
             return fail(MIORI_E_INVALID, "%s: a single rank holds all rows", op);
+    }
+    if (best_offset) {  // arg-max epilogue: scratch {key, arrivals}, candidates, winner
+        const size_t need = 16 + (size_t)(2 * g->world + 2) * 4;
+        if (M != 1) return fail(MIORI_E_INVALID, "%s: one activation row", op);
+        if (*best_offset % 16 != 0 || *best_offset + need > g->user_bytes)
+            return fail(MIORI_E_INVALID, "%s: %zu bytes at offset %zu do not fit the arena", op, need, *best_offset);
+        sh.best = reinterpret_cast<unsigned long long*>(g->mapped[g->rank] + PEER_CTL_BYTES + *best_offset);
     }
     rc = gemvtma::try_launch<BITS>(q, s, b, x, y_local, n_local, K, M, group, flags,
                                    (cudaStream_t)stream, sh);
@@ -308,6 +285,24 @@ MIORI_API int miori_gemv8_allgather(miori_peers* g, const void* q, const void* s
                                     uint32_t flags, void* stream) {
     return peers::gemv_allgather<8>("miori_gemv8_allgather", g, q, s, b, x, y_offset, n_local, row0,
                                     n_total, K, M, group, flags, stream);
+}
+
+MIORI_API size_t miori_gemv_argmax_bytes(int world) {
+    return world < 1 ? 0 : 16 + (size_t)(2 * world + 2) * 4;
+}
+
+MIORI_API int miori_gemv4_argmax(miori_peers* g, const void* q, const void* s, const void* b, const void* x,
+                                 size_t y_offset, size_t best_offset, uint32_t n_local, uint32_t row0,
+                                 uint32_t n_total, uint32_t K, uint32_t group, uint32_t flags, void* stream) {
+    return peers::gemv_allgather<4>("miori_gemv4_argmax", g, q, s, b, x, y_offset, n_local, row0, n_total, K, 1,
+                                    group, flags, stream, &best_offset);
+}
+
+MIORI_API int miori_gemv8_argmax(miori_peers* g, const void* q, const void* s, const void* b, const void* x,
+                                 size_t y_offset, size_t best_offset, uint32_t n_local, uint32_t row0,
+                                 uint32_t n_total, uint32_t K, uint32_t group, uint32_t flags, void* stream) {
+    return peers::gemv_allgather<8>("miori_gemv8_argmax", g, q, s, b, x, y_offset, n_local, row0, n_total, K, 1,
+                                    group, flags, stream, &best_offset);
 }
 
 MIORI_API int miori_allgather(miori_peers* g, const void* src, size_t y_offset, uint32_t M,

@@ -127,6 +127,66 @@ __device__ __forceinline__ void peer_finish(const PeerArgs& pa, uint32_t e) {
     ctl[CTL_COUNT] = 0u;
     st_relaxed_sys(ctl + CTL_EPOCH, e);
 }
+// Sharded arg-max: a candidate (value, index) per rank; larger value first, then the lower index
+// (the first maximum of the unsharded vector, as the host loop of src/engine.cpp:740-747).
+struct PeerBest {
+    float v;
+    uint32_t i;
+};
+__device__ __forceinline__ PeerBest peer_better(PeerBest a, PeerBest b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+// One thread of the whole grid: offer this rank's candidate to every peer, take theirs, reduce in
+// rank order.  `pairs` is this rank's [world][value, index] + winner [value, index] area in its
+// arena, `base` the same area's position in 4-byte units of the user area (where the peers'
+// packets land).  Returns the winner (this rank's candidate when there are no peers).
+__device__ __forceinline__ PeerBest peer_argmax_exchange(const PeerArgs& pa, uint32_t* pairs, size_t base,
+                                                         PeerBest mine) {
+    const uint32_t world = pa.world > 1u ? pa.world : 1u, rank = pa.world > 1u ? pa.rank : 0u;
+    pairs[2u * rank] = __float_as_uint(mine.v);
+    pairs[2u * rank + 1u] = mine.i;
+    PeerBest all = mine;
+    if (pa.world > 1u) {
+        const uint32_t e = peer_epoch(pa);
+        for (uint32_t p = 0; p < world; ++p) {
+            if (p == rank) continue;
+            uint8_t* arena = peer_arena(pa, p);
+            peer_send(peer_slot(pa, arena, e, base + 2u * rank), __float_as_uint(mine.v), e);
+            peer_send(peer_slot(pa, arena, e, base + 2u * rank + 1u), mine.i, e);
+        }
+        bool ok = true;
+        all = PeerBest{-INFINITY, 0xFFFFFFFFu};
+        for (uint32_t p = 0; p < world && ok; ++p) {
+            PeerBest b = mine;
+            if (p != rank) {
+                uint32_t vb = 0, ib = 0;
+                ok = peer_recv(pa, peer_slot(pa, pa.local, e, base + 2u * p), e, vb) &&
+                     peer_recv(pa, peer_slot(pa, pa.local, e, base + 2u * p + 1u), e, ib);
+                b = PeerBest{__uint_as_float(vb), ib};
+                pairs[2u * p] = vb;
+                pairs[2u * p + 1u] = ib;
+            }
+            if (ok) all = peer_better(all, b);
+        }
+        __threadfence();
+        st_relaxed_sys(peer_ctl(pa) + CTL_EPOCH, e);  // this thread does all the peer work of the launch
+    }
+    pairs[2u * world] = __float_as_uint(all.v);
+    pairs[2u * world + 1u] = all.i;
+    return all;
+}
+// Order-preserving 64-bit key of a candidate: the larger key is the larger value, and among equal
+// values the lower index; 0 stands for "none" (NaN never becomes a key).
+__device__ __forceinline__ unsigned long long peer_best_key(uint32_t value_bits, uint32_t index) {
+    const uint32_t ordered = (value_bits & 0x80000000u) ? ~value_bits : (value_bits | 0x80000000u);
+    return ((unsigned long long)ordered << 32) | (unsigned long long)(0xFFFFFFFFu - index);
+}
+__device__ __forceinline__ PeerBest peer_best_from_key(unsigned long long key) {
+    if (key == 0ull) return PeerBest{-INFINITY, 0xFFFFFFFFu};
+    const uint32_t ordered = (uint32_t)(key >> 32);
+    const uint32_t bits = (ordered & 0x80000000u) ? (ordered ^ 0x80000000u) : ~ordered;
+    return PeerBest{__uint_as_float(bits), 0xFFFFFFFFu - (uint32_t)key};
+}
 // The same for a kernel in which a single thread of the whole grid does the peer work: that
 // thread advances the launch number itself.
 __device__ __forceinline__ void peer_finish_single(const PeerArgs& pa, uint32_t e) {

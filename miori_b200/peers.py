@@ -102,6 +102,25 @@ class PeerGroup:
         w = 2 * self.world
         return int(pairs[w + 1:w + 2].view(torch.int32).item()), float(pairs[w].item())
 
+    def gemv_argmax(self, bits, q, s, b, x, y_offset, best_offset, row0, n_total, group=32, flags=0):
+        """This rank's rows of y = W x (one row of x) into its own arena, and the greedy pick over
+        the whole sharded vector left at best_offset on every rank (see gemv_argmax_result)."""
+        fn = lib.miori_gemv4_argmax if bits == 4 else lib.miori_gemv8_argmax
+        M, K = x.shape
+        if M != 1:
+            raise ValueError("gemv_argmax takes one activation row")
+        check(fn(self._h, q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), y_offset, best_offset,
+                 q.shape[0], row0, n_total, K, group, flags, self._stream()))
+
+    def gemv_argmax_bytes(self) -> int:
+        return lib.miori_gemv_argmax_bytes(self.world)
+
+    def gemv_argmax_result(self, best_offset):
+        """(index, value) left by gemv_argmax (call after synchronizing)."""
+        words = self.tensor(best_offset, (4 + 2 * self.world + 2,)).cpu()
+        w = 4 + 2 * self.world
+        return int(words[w + 1:w + 2].view(torch.int32).item()), float(words[w].item())
+
     def set_wait_us(self, microseconds: int):
         """Limit of the kernels' waits for a peer (default about a second)."""
         check(lib.miori_peers_set_wait_us(self._h, microseconds))

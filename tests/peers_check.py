@@ -127,6 +127,26 @@ def main() -> int:
             want_i = int(torch.nonzero(v.float() == want_v)[0, 0])
             expect(grp.argmax_result(offb) == (want_i, want_v), f"argmax exchange {dt} case {it}")
 
+    # the head and the greedy pick in one launch: every rank multiplies its rows, the ranks'
+    # best candidates meet, and every rank ends with the arg-max of the whole vector
+    q8[torch.arange(world) * rows + 5] = q8[3].clone()   # equal rows on every rank: ties across ranks
+    s8[torch.arange(world) * rows + 5] = s8[3].clone()
+    b8[torch.arange(world) * rows + 5] = b8[3].clone()
+    offy = grp.alloc(N * 4)
+    offb = grp.alloc(grp.gemv_argmax_bytes())
+    for obf in (0, miori_b200.OUT_BF16):
+        for it in range(3):
+            xh = synth.make_activation(1, K, seed=300 + it, device=dev)
+            grp.gemv_argmax(8, q8[r0:r0 + rows].contiguous(), s8[r0:r0 + rows].contiguous(),
+                            b8[r0:r0 + rows].contiguous(), xh, offy, offb, r0, N, group=G, flags=pdl | obf)
+            torch.cuda.synchronize()
+            whole = miori_b200.gemv8(q8, s8, b8, xh, group=G, flags=obf)[0].float()
+            want_i = int(torch.nonzero(whole == whole.max())[0, 0])
+            expect(grp.gemv_argmax_result(offb) == (want_i, float(whole.max())),
+                   f"gemv8_argmax bf16={bool(obf)} launch {it}")
+            mine = grp.tensor(offy, (1, N), torch.bfloat16 if obf else torch.float32)[0, r0:r0 + rows].float()
+            expect(torch.equal(mine, whole[r0:r0 + rows]), f"gemv8_argmax own rows bf16={bool(obf)} launch {it}")
+
     try:
         grp.status()
     except Exception as e:  # a bounded wait expired on this rank
