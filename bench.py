@@ -881,6 +881,35 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
     by = packed_bytes(N, K, 8, G)
     ex["config1_gemv8_m1_n131072_k2048"] = {"us": 1e3 * ms, "gbs": by / (ms * 1e-3) / 1e9,
                                             "frac_of_hbm_peak": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    # the same head followed by the greedy pick: two launches (gemv8, then arg-max) against one
+    # (the arg-max in the GEMV's epilogue), bf16 logits, both as replayed graphs of dependent launches
+    from miori_b200.peers import PeerGroup
+    grp1 = PeerGroup(0, 1, 1 << 20, dev)
+    off_y, off_b = grp1.alloc(N * 2), grp1.alloc(256)
+    yb = torch.empty((1, N), dtype=torch.bfloat16, device=dev)
+    hf = flags | miori_b200.OUT_BF16
+
+    def two_launches():
+        miori_b200.gemv8(q, s, b, x, group=G, flags=hf, out=yb)
+        return miori_b200.argmax(yb.view(-1), flags=flags)
+
+    def one_launch():
+        grp1.gemv_argmax(8, q, s, b, x, off_y, off_b, 0, N, group=G, flags=hf)
+    pick = {}
+    for name, fn in (("gemv8_then_argmax", two_launches), ("argmax_in_the_gemv_epilogue", one_launch)):
+        res = fn()
+        torch.cuda.synchronize()
+        gg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gg):
+            for _ in range(4):
+                fn()
+        pick[name + "_us"] = 1e3 * timed(gg.replay, 10) / 10 / 4
+        if res is not None:
+            pick["index"] = int(res[0].item())
+    torch.cuda.synchronize()
+    pick["same_token"] = grp1.gemv_argmax_result(off_b)[0] == pick.pop("index")
+    ex["config1_gemv8_m1_n131072_k2048"]["greedy_pick"] = pick
+    grp1.close()
     del q, s, b
     # long stream of 4-bit weights: M=1 over two distinct 151 MB matrices (N=131072, K=2048) -- the
     # kernel's rate once the fixed cost of a launch is amortised
