@@ -1,13 +1,13 @@
 // Weight-streaming GEMV with the weights staged through shared memory by TMA.
 //
-// One CTA per SM owns a contiguous range of 16-row tiles.  Each slab -- 16 rows x 1 KiB of
+// One CTA per SM (two for long streams) owns every gridDim-th 16-row tile.  Each slab -- 16 rows x 1 KiB of
 // packed codes plus the rows' scales and biases, three cp.async.bulk.tensor requests -- goes
 // into a ring of shared-memory stages; completion is counted in bytes on a "full" mbarrier
 // per stage and consumers hand stages back through an "empty" mbarrier.  The ring is filled
 // BEFORE the kernel waits for its predecessor (programmatic dependent launch): weights are
-// immutable, so while kernel i reduces and stores, kernel i+1 already has its weights in
-// flight or resident and HBM stays busy across launch boundaries.  After the wait the CTA
-// stages x (see gemv_mma.cuh for the arithmetic and the k permutation).
+// immutable, so a CTA that starts as its predecessor's CTA exits has its first slabs in flight
+// while the grids hand over.  After the wait the CTA stages x (see gemv_mma.cuh for the arithmetic
+// and the k permutation).
 //
 // The 16 warps work in four independent groups of four; a group owns whole tiles, each of
 // its warps multiplies 4 of the 16 steps of a slab out of shared memory, and the four
