@@ -201,9 +201,9 @@ int miori_gemm_bf16_strided(const void* A, uint32_t lda, const void* B, uint32_t
  * no workspace.  What the reference's wide-batch path (gemm_mpp on the bf16 cache) computes for
  * the batch sizes of a decode step; a row's value depends neither on the grid nor on M within a
  * class of batch sizes (1..8, 9..16, 17..32 rows).  Every
- * warp keeps its share of the activations in registers, which bounds K: K <= 2048 for 17..32 rows,
- * K <= 4096 for 9..16 rows, K <= 8192 up to 8 rows; beyond that MIORI_E_INVALID: use
- * miori_gemm_bf16_cache there. */
+ * warp keeps its share of the activations in registers (K <= 2048 for 17..32 rows, K <= 4096 for
+ * 9..16 rows, K <= 8192 up to 8 rows) or, for longer rows up to K = 8192, streams it from L2 a few
+ * k-slabs ahead of its use; beyond K = 8192 MIORI_E_INVALID: use miori_gemm_bf16_cache there. */
 int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, uint32_t M, uint32_t N, uint32_t K,
                           uint32_t flags, void* stream);
 

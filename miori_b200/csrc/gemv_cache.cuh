@@ -59,13 +59,19 @@ size_t smem_bytes(uint32_t nstage) {
     return 128 + (size_t)nstage * STAGE_BYTES + Cfg<NT>::RED_BYTES;
 }
 
+constexpr int X_AHEAD = 3;  // streamed x: k-slabs between the load of a fragment and its use
+
 // SLABS = ceil(K / 512) is a template parameter so that the x fragments index registers.
-template <int NT, int SLABS, bool OUT_BF16>
+// STREAM: the fragments are loaded per tile, X_AHEAD slabs ahead, instead of once per CTA.
+template <int NT, int SLABS, bool OUT_BF16, bool STREAM = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __restrict__ x,
                   void* __restrict__ y, uint32_t N, uint32_t K, uint32_t M, uint32_t nstage) {
     constexpr uint32_t slabs = SLABS;
-    static_assert(NT * SLABS <= MAX_FRAGS, "x fragments held in registers");
+    constexpr int XF = STREAM ? X_AHEAD + 1 : SLABS;  // fragment sets held per lane
+    static_assert(NT * XF <= (STREAM ? 20 : MAX_FRAGS), "x fragments held in registers");
+    // a slab's slot is s % XF in every tile, so the ring must divide the slabs of a tile
+    static_assert(!STREAM || (SLABS > X_AHEAD && SLABS % XF == 0), "streaming is for long rows");
     using C = Cfg<NT>;
     using namespace gemvmma;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -116,19 +122,20 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
     // this lane's B fragments: 16 bytes of activation row 8 (warp % NT) + g at
     // k = 512 s + 32 (NT (warp / NT) + i) + 8 t for the NT steps i of the warp's k part
     const uint32_t set = warp % (uint32_t)NT, kpart = warp / (uint32_t)NT;
-    uint4 xf[SLABS][NT];
-    {
+    uint4 xf[XF][NT];
+    // the fragments of k-slab s into slot s % XF
+    auto load_x = [&](int s) {
         const uint32_t g = lane >> 2, t = lane & 3u, m = 8u * set + g;
 #pragma unroll
-        for (int s = 0; s < SLABS; ++s)
+        for (int i = 0; i < NT; ++i) {
+            const uint32_t k = (uint32_t)s * KS + (kpart * NT + i) * 32u + t * 8u;
+            xf[s % XF][i] = make_uint4(0u, 0u, 0u, 0u);
+            if (warp < WARPS && m < M && k < K)  // K is a multiple of 8: whole pieces
+                xf[s % XF][i] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + k));
+        }
+    };
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                const uint32_t k = (uint32_t)s * KS + (kpart * NT + i) * 32u + t * 8u;
-                xf[s][i] = make_uint4(0u, 0u, 0u, 0u);
-                if (warp < WARPS && m < M && k < K)  // K is a multiple of 8: whole pieces
-                    xf[s][i] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + k));
-            }
-    }
+    for (int s = 0; s < (STREAM ? X_AHEAD : SLABS); ++s) load_x(s);
     __syncthreads();  // barriers initialised before anyone waits on them
 
     if (producer) {
@@ -152,6 +159,10 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int s = 0; s < SLABS; ++s) {
+                if constexpr (STREAM) {  // the fragments X_AHEAD slabs on (of the next tile past the last slab)
+                    if (s + X_AHEAD < SLABS) load_x(s + X_AHEAD);
+                    else if (ti + 1u < my_tiles) load_x(s + X_AHEAD - SLABS);
+                }
                 if (ok) {
                     ok = mbar_wait(smem_addr(&full_bars[stage]), parity, &abort_flag, 0x20);
                     ok = __all_sync(0xFFFFFFFFu, ok);
@@ -162,8 +173,8 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
                     for (int i = 0; i < NT; ++i) {
                         const uint4 q0 = gemvtma::lds128(st + (uint32_t)i * 64u);
                         const uint4 q1 = gemvtma::lds128(st + (uint32_t)i * 64u + 8u * (uint32_t)PITCH);
-                        mma_bf16(acc, q0.x, q1.x, q0.y, q1.y, xf[s][i].x, xf[s][i].y);
-                        mma_bf16(acc2, q0.z, q1.z, q0.w, q1.w, xf[s][i].z, xf[s][i].w);
+                        mma_bf16(acc, q0.x, q1.x, q0.y, q1.y, xf[s % XF][i].x, xf[s % XF][i].y);
+                        mma_bf16(acc2, q0.z, q1.z, q0.w, q1.w, xf[s % XF][i].z, xf[s % XF][i].w);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_addr(&empty_bars[stage]));  // stage consumed
@@ -203,13 +214,14 @@ gemv_cache_kernel(const __grid_constant__ CUtensorMap tmap_w, const uint16_t* __
 
 // Try the narrow-batch kernel; returns 1 if the problem is outside its range (nothing launched).
 inline int try_launch(const void* x, const void* cache, void* y, uint32_t M, uint32_t N, uint32_t K,
-                      uint32_t flags, cudaStream_t stream) {
+                      uint32_t flags, cudaStream_t stream_) {
     if (M == 0 || M > 32 || K % 8 != 0) return 1;
     const uint32_t slabs = (K + KS - 1) / KS;
     const uint32_t nt = M <= 8 ? 1 : M <= 16 ? 2 : 4;
     // instantiated slab counts; a slab past the end of K is zero-filled by TMA and multiplies zeros
     const uint32_t slabs_t = slabs <= 1 ? 1 : slabs <= 2 ? 2 : slabs <= 4 ? 4 : slabs <= 8 ? 8 : 16;
-    if (slabs > 16 || slabs_t * nt > (uint32_t)MAX_FRAGS) return 1;  // the activations would not fit the registers
+    if (slabs > 16) return 1;
+    const bool stream = slabs_t * nt > (uint32_t)MAX_FRAGS;  // a row's fragments do not fit the registers
     const uint32_t tiles = (N + 15u) / 16u;
     const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)sm_count());
     const uint32_t nstage =
@@ -230,11 +242,23 @@ inline int try_launch(const void* x, const void* cache, void* y, uint32_t M, uin
         auto kern = gemv_cache_kernel<NTV, SL, OB>;                                               \
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (e == cudaSuccess)                                                                     \
-            e = launch(kern, dim3(grid), dim3(THREADS), smem, stream, pdl, tw,                    \
+            e = launch(kern, dim3(grid), dim3(THREADS), smem, stream_, pdl, tw,                   \
                        static_cast<const uint16_t*>(x), y, N, K, M, nstage);                      \
     } while (0)
 #define MIORI_CACHE_SL(NTV, SL) do { if (bf16) MIORI_CACHE_LAUNCH(NTV, SL, true); else MIORI_CACHE_LAUNCH(NTV, SL, false); } while (0)
-    if (nt == 1) {
+#define MIORI_CACHE_STREAM(NTV, SL)                                                               \
+    do {                                                                                          \
+        auto kern = bf16 ? gemv_cache_kernel<NTV, SL, true, true> : gemv_cache_kernel<NTV, SL, false, true>; \
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        if (e == cudaSuccess)                                                                     \
+            e = launch(kern, dim3(grid), dim3(THREADS), smem, stream_, pdl, tw,                   \
+                       static_cast<const uint16_t*>(x), y, N, K, M, nstage);                      \
+    } while (0)
+    if (stream) {
+        if (nt == 2) MIORI_CACHE_STREAM(2, 16);
+        else if (slabs_t == 8) MIORI_CACHE_STREAM(4, 8);
+        else MIORI_CACHE_STREAM(4, 16);
+    } else if (nt == 1) {
         if (slabs_t == 1) MIORI_CACHE_SL(1, 1); else if (slabs_t == 2) MIORI_CACHE_SL(1, 2);
         else if (slabs_t == 4) MIORI_CACHE_SL(1, 4); else if (slabs_t == 8) MIORI_CACHE_SL(1, 8);
         else MIORI_CACHE_SL(1, 16);
@@ -245,6 +269,7 @@ inline int try_launch(const void* x, const void* cache, void* y, uint32_t M, uin
         if (slabs_t == 1) MIORI_CACHE_SL(4, 1); else if (slabs_t == 2) MIORI_CACHE_SL(4, 2);
         else MIORI_CACHE_SL(4, 4);
     }
+#undef MIORI_CACHE_STREAM
 #undef MIORI_CACHE_SL
 #undef MIORI_CACHE_LAUNCH
     if (e != cudaSuccess) return cuda_fail(e, "gemv_cache launch");

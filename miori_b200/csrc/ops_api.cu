@@ -121,8 +121,7 @@ MIORI_API int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, u
         return fail(MIORI_E_INVALID, "%s: x, cache and y must be 16-byte aligned", op);
     const int rc = gemvcache::try_launch(x, cache, y, M, N, K, flags, (cudaStream_t)stream);
     if (rc == 1)
-        return fail(MIORI_E_INVALID, "%s: M=%u rows of K=%u are more activations than the kernel keeps in "
-                    "registers (use miori_gemm_bf16_cache)", op, M, K);
+        return fail(MIORI_E_INVALID, "%s: K=%u is beyond the kernel's 8192 (use miori_gemm_bf16_cache)", op, K);
     return rc;
 }
 
@@ -130,8 +129,8 @@ MIORI_API int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, u
 // bf16 cache, 2 = tcgen05 GEMM on the bf16 cache.  Measured on B200 in chains of dependent
 // launches (us per launch, 2048 -> 3072 / 2048 -> 2048 / 8192 -> 2048 / 2048 -> 16384):
 //   M = 8:  packed 4.4 / 3.9 / 8.9 / 10.5, narrow 4.1 / 3.2 / 7.6 / 11.8
-//   M = 16: packed 5.3 / 4.7 / 82 / 12.6,  narrow 4.3 / 3.3 / -- / 11.9,  GEMM 8.9 / 7.6 / 12.6 / 15.7
-//   M = 32: packed 10.8 / 7.1 / 162 / 32,  narrow 5.6 / 4.3 / -- / 17.0,  GEMM 8.6 / 7.8 / 12.8 / 15.8
+//   M = 16: packed 5.3 / 4.7 / 82 / 12.6,  narrow 4.4 / 3.3 / 9.2 / 12.1,  GEMM 8.9 / 7.6 / 12.6 / 15.9
+//   M = 32: packed 10.8 / 7.1 / 162 / 32,  narrow 5.6 / 4.4 / 14.6 / 17.4, GEMM 8.6 / 7.8 / 12.8 / 16.0
 // Up to four rows stay on the packed weights with fp32 dequantization, as in the reference
 // (src/batch.cpp:223-230 cuts over to the cache above four rows).  Above that the cache is used
 // when given: by the narrow-batch kernel while the projection is short (at most two 16-row tiles
@@ -141,10 +140,16 @@ MIORI_API int miori_gemv_bf16_cache(const void* x, const void* cache, void* y, u
 static int linear4_route(uint32_t M, uint32_t N, uint32_t K, bool has_cache) {
     if (M <= 4 || !has_cache) return 0;
     const uint32_t tiles = (N + 15u) / 16u, slabs = (K + 511u) / 512u;
-    const uint32_t frags = (slabs <= 1 ? 1u : slabs <= 2 ? 2u : slabs <= 4 ? 4u : slabs <= 8 ? 8u : 16u) *
-                           (M <= 8 ? 1u : M <= 16 ? 2u : 4u);
-    const bool fits = slabs <= 16u && frags <= (uint32_t)gemvcache::MAX_FRAGS && K % 8 == 0;
-    if (fits && (tiles <= 2u * (uint32_t)sm_count() || (M > 8 && M <= 16))) return 1;
+    const uint32_t nt = M <= 8 ? 1u : M <= 16 ? 2u : 4u;
+    const uint32_t frags = (slabs <= 1 ? 1u : slabs <= 2 ? 2u : slabs <= 4 ? 4u : slabs <= 8 ? 8u : 16u) * nt;
+    const bool short_proj = tiles <= 2u * (uint32_t)sm_count();
+    if (slabs <= 16u && K % 8 == 0) {
+        // activations resident in registers: short projections, and 9..16 rows of any width
+        if (frags <= (uint32_t)gemvcache::MAX_FRAGS && (short_proj || nt == 2u)) return 1;
+        // activations streamed per tile (long rows): pays up to 16 rows on short projections
+        // (8192 -> 2048 at 16 rows: 9.2 us against 12.6 us for the GEMM; at 32 rows 14.6 against 12.8)
+        if (frags > (uint32_t)gemvcache::MAX_FRAGS && short_proj && nt == 2u) return 1;
+    }
     if (M <= 8) return 0;
     return 2;
 }

@@ -157,7 +157,8 @@ def test_linear_dispatch(port, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(32, 2048, 2048), (16, 3072, 2048), (5, 1000, 512), (1, 16, 64), (9, 17, 1096),
                                    (16, 2048, 4096), (24, 640, 2048), (32, 16384, 2048), (31, 100, 2048),
-                                   (8, 512, 8192), (32, 256, 1536)])
+                                   (8, 512, 8192), (32, 256, 1536), (16, 2048, 8192), (32, 2048, 8192),
+                                   (32, 100, 4096), (24, 700, 6144), (9, 4000, 8192)])
 def test_narrow_batch_cache_kernel(port, M, N, K):
     """miori_gemv_bf16_cache against the oracle's exact product over the bit-exact cache, with the
     GEMM's tolerance; a row's value does not depend on M within a class of batch sizes (1..8,
@@ -179,12 +180,12 @@ def test_narrow_batch_cache_kernel(port, M, N, K):
 
 def test_narrow_batch_cache_kernel_random_shapes():
     """Sixty seeded random shapes -- N from 1 (ragged tiles, fewer tiles than SMs) to a few thousand,
-    K any multiple of 8 within the kernel's range (ragged last slab, K shorter than one MMA step's
-    32), every batch class -- against a plain fp32 product of the same bf16 operands."""
+    K any multiple of 8 up to 8192 (ragged last slab, K shorter than one MMA step's 32, rows whose
+    fragments are resident in registers and rows that are streamed), every batch class -- against a plain fp32 product of the same bf16 operands."""
     g = torch.Generator().manual_seed(1234)
     for case in range(60):
         M = int(torch.randint(1, 33, (1,), generator=g))
-        kmax = 8192 if M <= 8 else 4096 if M <= 16 else 2048
+        kmax = 8192
         K = 8 * int(torch.randint(1, kmax // 8 + 1, (1,), generator=g))
         N = int(torch.randint(1, 3000, (1,), generator=g)) if case % 3 else int(torch.randint(1, 40, (1,), generator=g))
         W = (torch.randn((N, K), generator=g) * 0.05).to(torch.bfloat16).to(DEV)
@@ -197,12 +198,12 @@ def test_narrow_batch_cache_kernel_random_shapes():
 
 
 def test_narrow_batch_cache_kernel_refuses_what_it_cannot_hold():
-    _, _, _, cache = _weights(64, 8192, 64, seed=3)
-    x = synth.make_activation(16, 8192, seed=4, device=DEV)
-    with pytest.raises(miori_b200.MioriError, match="registers"):
+    _, _, _, cache = _weights(64, 8192 + 512, 64, seed=3)
+    x = synth.make_activation(16, 8192 + 512, seed=4, device=DEV)
+    with pytest.raises(miori_b200.MioriError, match="8192"):
         miori_b200.gemv_bf16_cache(x, cache, 64)
     with pytest.raises(miori_b200.MioriError):
-        miori_b200.gemv_bf16_cache(synth.make_activation(33, 64, seed=1, device=DEV), cache, 64)
+        miori_b200.gemv_bf16_cache(synth.make_activation(33, 64, seed=1, device=DEV), cache[:64 * 64], 64)
 
 
 # ---- strided bf16 GEMM (the reference's gemm_naive, shaders/ops.metal:199-251) ---------------
