@@ -963,6 +963,49 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
                                "layer_fused_us": sum(v["fused_us"] for v in fused.values()),
                                "how": "CUDA graphs of PDL launches; the unfused pair is the default GEMV after "
                                       "miori_rmsnorm, the fused one miori_gemv4_rmsnorm (tcgen05 kernel)"}
+    # SiLU x up behind the fused gate + up projection (2048 -> 2 x 8192): GEMV + activation kernel
+    # against the GEMV with the activation as its epilogue, over a pool of distinct weights (> L2)
+    N, K = 16384, 2048
+    pool = [synth.make_weight(N, K, 4, G, seed=800 + i, device=dev) for i in range(24)]
+    gated = {}
+    for M in (1, 4, 8, 16):
+        xg = synth.make_activation(M, K, seed=5, device=dev)
+        yf = torch.empty((M, N), device=dev)
+        act = torch.empty((M, N // 2), dtype=torch.bfloat16, device=dev)
+
+        g1 = torch.empty((M, N // 2), device=dev)
+        u1 = torch.empty((M, N // 2), device=dev)
+
+        def three_launches():  # the reference's structure: w1, w3, then the activation (src/engine.cpp)
+            for q, s, b in pool:
+                miori_b200.gemv4(q[:N // 2], s[:N // 2], b[:N // 2], xg, group=G, flags=flags, out=g1)
+                miori_b200.gemv4(q[N // 2:], s[N // 2:], b[N // 2:], xg, group=G, flags=flags, out=u1)
+                miori_b200.silu_mul(g1, u1, flags=flags, out=act)
+
+        def two_launches():  # one row only: gate and up are the two halves of the fused projection's row
+            for q, s, b in pool:
+                miori_b200.gemv4(q, s, b, xg, group=G, flags=flags, out=yf)
+                miori_b200.silu_mul(yf[0, :N // 2], yf[0, N // 2:], flags=flags, out=act[0])
+
+        def gated_gemv():
+            for q, s, b in pool:
+                miori_b200.gemv4_silu(q, s, b, xg, group=G, flags=flags, out=act)
+        res = {}
+        for name, fn in (("w1_w3_silu_mul_us", three_launches), ("gate_up_silu_mul_us", two_launches),
+                         ("fused_us", gated_gemv)):
+            if fn is two_launches and M > 1:
+                continue
+            fn()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            res[name] = 1e3 * timed(g.replay, 10) / 10 / len(pool)
+        gated[f"M{M}"] = res
+    del pool
+    ex["silu_fusion_gate_up"] = {"per_m": gated,
+                                 "how": "CUDA graphs of PDL launches; miori_gemv4 on w1 and on w3 then miori_silu_mul (three "
+                                        "launches), miori_gemv4 on the fused weights then miori_silu_mul (two, one row), "
+                                        "and miori_gemv4_silu (TMA + mma.sync kernel, gated epilogue)"}
     # config 3: prefill GEMM M=1024 on the bf16 cache + cache build.  Each shape runs over a
     # pool of distinct caches larger than L2 (weights come from HBM, as in a real prefill where
     # consecutive layers evict each other), one CUDA graph of PDL launches per shape.

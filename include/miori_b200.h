@@ -318,6 +318,15 @@ int miori_embed8(const void* q, const void* s, const void* b, const void* tokens
 /* Index (u32) and, if out_value is not NULL, value (fp32) of the largest of n elements (fp32, or
  * bf16 with MIORI_OUT_BF16); ties go to the lowest index (src/engine.cpp:740-747). */
 int miori_argmax(const void* v, uint32_t n, uint32_t flags, void* out_index, void* out_value, void* stream);
+/* miori_gemv4 over the fused gate + up weights (w1 rows [0, N/2), then w3 rows [N/2, N)) with
+ * silu_mul (shaders/ops.metal:129-139) as its epilogue: y bf16 [M][N/2], y[m][i] = bf16(silu(g) * u)
+ * for g, u the fp32 results of rows i and N/2 + i, bit for bit what miori_gemv4 followed by
+ * miori_silu_mul gives.  Saves the activation's launch and the fp32 round trip of 2 N values per
+ * row (docs/MILESTONES.md:87, "SiLU x up epilogue").  N a multiple of 16, M <= 16 (wider batches
+ * go through the bf16 cache, whose GEMM has no such epilogue); runs on the TMA + mma.sync kernel,
+ * shapes it does not take get MIORI_E_INVALID. */
+int miori_gemv4_silu(const void* q, const void* s, const void* b, const void* x, void* y, uint32_t N,
+                     uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream);
 /* miori_gemv4 / miori_gemv8 with the RMSNorm of the activations fused into their staging:
  * y = W * bf16(rmsnorm(x)), x fp32 [M][K], gamma bf16 [K].  Saves the norm's launch and the
  * round trip of its output (the fusion the reference planned, docs/MILESTONES.md:87).  Runs on

@@ -273,7 +273,8 @@ __device__ __forceinline__ unsigned long long gtimer() {
 // the candidates meet in a 64-bit atomic maximum, and the CTA that finishes last exchanges this
 // rank's best with the peers (peers.cuh: peer_argmax_exchange), so the kernel ends with the winning
 // token on every rank and nothing else has crossed NVLink.
-template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR, bool ARGMAX = false>
+template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR, bool ARGMAX = false,
+          bool GATED = false>
 __global__ void __launch_bounds__(THREADS, (NT == 1 && !ROOMY) ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_s,
@@ -284,6 +285,10 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const PeerArgs pa, uint32_t n_total, uint32_t row0, size_t y_off,
                 unsigned long long* __restrict__ best) {
     static_assert(!ARGMAX || SHARDED, "the arg-max epilogue lives in the sharded instantiation");
+    // GATED: the weight rows are a gate half [0, N/2) and an up half [N/2, N) (the fused w1/w3
+    // projection); a tile is eight rows of each, so that after the tile's reduction one thread
+    // pair holds gate and up of the same output, and y is bf16 [M][N/2] of silu(gate) * up.
+    static_assert(!GATED || (BITS == 4 && OUT_BF16 && !SHARDED), "the gated epilogue: 4-bit, bf16 out, one GPU");
     using namespace gemvmma;
     const uint32_t nstage = ngrp * nsg;  // every active group owns a private ring of nsg stages
     constexpr int CW = 128 / BITS;          // codes per 16-byte chunk
@@ -369,7 +374,25 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint32_t vt = p_set0 + p_gi;
             const uint32_t row = (blockIdx.x + (vt >> kshift) * gridDim.x) * 16u;
             const uint32_t ks = (vt & (kpar - 1u)) + (p_ks << kshift);
-            if (linear) {
+            if (GATED && linear) {  // N is a multiple of 16: eight whole rows of each half
+                const uint32_t r8 = row >> 1, up8 = (N >> 1) + r8;
+                mbar_expect_tx(bar, 16u * (qpitch + 4u * spitch));
+                bulk_g2s(dst, qlin + (size_t)r8 * qpitch, 8u * qpitch, bar);
+                bulk_g2s(dst + 8u * qpitch, qlin + (size_t)up8 * qpitch, 8u * qpitch, bar);
+                bulk_g2s(dst + Q_BYTES, slin + (size_t)r8 * spitch, 16u * spitch, bar);
+                bulk_g2s(dst + Q_BYTES + 16u * spitch, slin + (size_t)up8 * spitch, 16u * spitch, bar);
+                bulk_g2s(dst + Q_BYTES + SB_BYTES, blin + (size_t)r8 * spitch, 16u * spitch, bar);
+                bulk_g2s(dst + Q_BYTES + SB_BYTES + 16u * spitch, blin + (size_t)up8 * spitch, 16u * spitch, bar);
+            } else if (GATED) {  // the tensor maps' boxes are eight rows high
+                const int r8 = (int)(row >> 1), up8 = (int)((N >> 1) + (row >> 1));
+                mbar_expect_tx(bar, stage_tx);
+                tma_load_2d(dst, &tmap_q, (int)(ks * (ROW_BYTES / 4)), r8, bar);
+                tma_load_2d(dst + 8u * ROW_BYTES, &tmap_q, (int)(ks * (ROW_BYTES / 4)), up8, bar);
+                tma_load_2d(dst + Q_BYTES, &tmap_s, (int)(ks * gps), r8, bar);
+                tma_load_2d(dst + Q_BYTES + 16u * gps, &tmap_s, (int)(ks * gps), up8, bar);
+                tma_load_2d(dst + Q_BYTES + SB_BYTES, &tmap_b, (int)(ks * gps), r8, bar);
+                tma_load_2d(dst + Q_BYTES + SB_BYTES + 16u * gps, &tmap_b, (int)(ks * gps), up8, bar);
+            } else if (linear) {
                 const uint32_t nrows = min(16u, N - row);  // rows past N keep stale (unused) data
                 mbar_expect_tx(bar, nrows * (qpitch + 4u * spitch));
                 bulk_g2s(dst, qlin + (size_t)row * qpitch, nrows * qpitch, bar);
@@ -451,6 +474,14 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
         }
     };
+
+    // GATED: y[m][row] = bf16(silu(gate) * up) of the N/2-column output, with the arithmetic of the
+    // stand-alone activation kernel (shaders/ops.metal:129-139)
+    auto store_gated = [&](uint32_t m, uint32_t row, float gate, float up) {
+        const float sg = gate / (1.0f + expf(-gate));
+        reinterpret_cast<uint16_t*>(y)[(size_t)m * (N >> 1) + row] = (uint16_t)float_to_bf16_bits(sg * up);
+    };
+    (void)store_gated;
 
     // one-pass staging where it measured faster: one slab of K, and either the roomy
     // instantiation or at most two staged rows
@@ -735,12 +766,21 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (uint32_t base = 0; base < 16u * MP * 4u; base += 128u) {
             const uint32_t idx = base + gt;
             const uint32_t o = idx >> 2, w = idx & 3u;  // output o = m*16 + r, partial of warp w
-            const uint32_t r = o & 15u, m = o >> 4;
+            // GATED enumerates the outputs as o = (m*8 + r')*2 + half, tile row r = r' + 8 half:
+            // gate and up of an output sit in neighbouring quads (neighbouring threads below)
+            const uint32_t r = GATED ? ((o >> 1) & 7u) + ((o & 1u) << 3) : o & 15u, m = o >> 4;
             float v = buf[(size_t)w * WS + r * MP + m];
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
             const uint32_t row = tile * 16u + r;
-            if (kpar > 1u) {
+            if constexpr (GATED) {
+                const float up = __shfl_down_sync(0xFFFFFFFFu, v, 4);
+                if (kpar > 1u) {
+                    if (w == 0) kred[((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP) + o] = v;
+                } else if (w == 0 && (o & 1u) == 0u && m < M && ok) {
+                    store_gated(m, tile * 8u + r, v, up);
+                }
+            } else if (kpar > 1u) {
                 if (w == 0) kred[((size_t)(tile_it & 1u) * GROUPS + grp) * (16 * MP) + o] = v;
             } else if (w == 0 && m < M && row < N && ok) {
                 store_out(m, row, v);
@@ -754,8 +794,14 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 for (uint32_t o = gt; o < 16u * MP; o += 128u) {
                     float v = kr[o];
                     for (uint32_t j = 1; j < kpar; ++j) v += kr[(size_t)j * (16 * MP) + o];
-                    const uint32_t r = o & 15u, m = o >> 4, row = tile * 16u + r;
-                    if (m < M && row < N && ok) store_out(m, row, v);
+                    if constexpr (GATED) {  // 16 MP is a multiple of 32: whole warps run this loop
+                        const float up = __shfl_down_sync(0xFFFFFFFFu, v, 1);
+                        const uint32_t m = o >> 4;
+                        if ((o & 1u) == 0u && m < M && ok) store_gated(m, tile * 8u + ((o >> 1) & 7u), v, up);
+                    } else {
+                        const uint32_t r = o & 15u, m = o >> 4, row = tile * 16u + r;
+                        if (m < M && row < N && ok) store_out(m, row, v);
+                    }
                 }
             }
         }
@@ -829,6 +875,9 @@ struct Shard {
     // arg-max epilogue (one activation row): 16 bytes of zeroed scratch {key, arrivals} followed by
     // the (2 world + 2) words of the candidates and the winner, inside the local arena; null: off
     unsigned long long* best = nullptr;
+    // gated epilogue (4-bit weights, one GPU): rows [0, N/2) are the gate and [N/2, N) the up
+    // projection, y is bf16 [M][N/2] of silu(gate) * up
+    bool gated = false;
 };
 
 // Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
@@ -894,21 +943,22 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     // K within one slab: plain bulk copies (rows of a tile are contiguous); else tiled TMA
     const bool linear = K <= (uint32_t)KC && !(flags & MIORI_TUNE_GEMV_TILED);
     CUtensorMap tq, ts, tb;
+    const uint32_t box_rows = sh.gated ? 8 : 16;  // gated: a tile is two boxes, one from each half
     int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)K * BITS / 32, N,
-                          ROW_BYTES / 4, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
+                          ROW_BYTES / 4, box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    rc = make_tmap_2d(&ts, s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, K / group, N, KC / group, 16,
+    rc = make_tmap_2d(&ts, s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, K / group, N, KC / group, box_rows,
                       CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, K / group, N, KC / group, 16,
+    rc = make_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, K / group, N, KC / group, box_rows,
                       CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     const uint8_t* ql = linear ? reinterpret_cast<const uint8_t*>(q) : nullptr;
     cudaError_t e = cudaSuccess;
-#define MIORI_TMA_LAUNCH(OB, SH, AM)                                                             \
+#define MIORI_TMA_LAUNCH(OB, SH, AM, GT)                                                         \
     do {                                                                                         \
-        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM>          \
-                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM>;           \
+        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM, GT>      \
+                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM, GT>;       \
         e = cudaSuccess;                                                                         \
         if (smem_l > 48 * 1024)                                                                  \
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_l); \
@@ -926,16 +976,22 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     const bool placed = sharded || argmax;  // y is a slice of an n_total-row output
     const bool roomy = NT == 1 && plan.roomy;
     const size_t smem_l = plan.pad ? std::max<size_t>(smem, 120 * 1024) : smem;
+    if (sh.gated && (BITS != 4 || sharded || argmax || N % 16 != 0))
+        return fail(MIORI_E_INVALID, "the gated epilogue takes 4-bit weights with N a multiple of 16 on one GPU");
     if constexpr (can_argmax) {
         if (argmax) {
-            if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true, true, true); else MIORI_TMA_LAUNCH(false, true, true);
+            if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true, true, true, false);
+            else MIORI_TMA_LAUNCH(false, true, true, false);
         }
     }
-    if (!argmax) {
+    if constexpr (BITS == 4) {
+        if (sh.gated) MIORI_TMA_LAUNCH(true, false, false, true);
+    }
+    if (!argmax && !sh.gated) {
         if (flags & MIORI_OUT_BF16) {
-            if (sharded) MIORI_TMA_LAUNCH(true, true, false); else MIORI_TMA_LAUNCH(true, false, false);
+            if (sharded) MIORI_TMA_LAUNCH(true, true, false, false); else MIORI_TMA_LAUNCH(true, false, false, false);
         } else {
-            if (sharded) MIORI_TMA_LAUNCH(false, true, false); else MIORI_TMA_LAUNCH(false, false, false);
+            if (sharded) MIORI_TMA_LAUNCH(false, true, false, false); else MIORI_TMA_LAUNCH(false, false, false, false);
         }
     }
 #undef MIORI_TMA_LAUNCH

@@ -99,6 +99,26 @@ int gemv_rmsnorm_entry(const char* op, const void* q, const void* s, const void*
 }
 }  // namespace
 
+MIORI_API int miori_gemv4_silu(const void* q, const void* s, const void* b, const void* x, void* y, uint32_t N,
+                               uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream) {
+    const char* op = "miori_gemv4_silu";
+    int rc = check_quant_args(op, q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!x || !y) return fail(MIORI_E_INVALID, "%s: null activation pointer", op);
+    // 17..32 staged rows do not fit the kernel's shared memory at any K
+    if (M == 0 || M > 16) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..16", op, M);
+    if (!aligned16(x)) return fail(MIORI_E_INVALID, "%s: x must be 16-byte aligned", op);
+    if (N % 16 != 0)
+        return fail(MIORI_E_INVALID, "%s: N=%u (gate rows then up rows) must be a multiple of 16", op, N);
+    gemvtma::Shard sh;
+    sh.gated = true;
+    rc = gemvtma::try_launch<4>(q, s, b, x, y, N, K, M, group, flags | MIORI_OUT_BF16, (cudaStream_t)stream, sh);
+    if (rc == 1)
+        return fail(MIORI_E_INVALID, "%s: shape N=%u K=%u M=%u group=%u is outside the fused kernel's range "
+                    "(run the plain GEMV and miori_silu_mul instead)", op, N, K, M, group);
+    return rc;
+}
+
 MIORI_API int miori_gemv4_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
                                   float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
                                   uint32_t flags, void* stream) {

@@ -213,3 +213,19 @@ def gemv4_rmsnorm(q, s, b, x, gamma, eps, group=32, flags=0, out=None):
 
 def gemv8_rmsnorm(q, s, b, x, gamma, eps, group=32, flags=0, out=None):
     return _gemv_rmsnorm(lib.miori_gemv8_rmsnorm, 4, q, s, b, x, gamma, eps, group, flags, out)
+
+
+def gemv4_silu(q, s, b, x, group=32, flags=0, out=None):
+    """bf16(silu(gate) * up) [M][N/2] for the fused gate + up weights q [N][K/8] (gate rows first):
+    gemv4 with silu_mul as its epilogue."""
+    _need_cuda(q, s, b, x)
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    M, K = x.shape
+    N = q.shape[0]
+    if q.shape[1] * 8 != K:
+        raise ValueError(f"q has {q.shape[1]} words per row, expected {K // 8}")
+    y = out if out is not None else torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    check(lib.miori_gemv4_silu(q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), y.data_ptr(), N, K, M,
+                               group, flags, _stream()))
+    return y

@@ -106,6 +106,12 @@ def test_neighbor_and_narrow_batch_entries_reject_bad_arguments():
     # a K beyond the kernel's range: refused on the host, nothing launched
     assert lib.miori_gemv_bf16_cache(ok, ok, ok, 32, 64, 8192 + 8, 0, None) == -1
     assert b"8192" in lib.miori_last_error()
+    # the gated GEMV: N holds the gate rows and then as many up rows, eight of each per tile
+    assert lib.miori_gemv4_silu(ok, ok, ok, ok, ok, 24, 64, 1, 32, 0, None) == -1
+    assert b"multiple of 16" in lib.miori_last_error()
+    assert lib.miori_gemv4_silu(ok, ok, ok, ok, ok, 32, 64, 33, 32, 0, None) == -1
+    assert lib.miori_gemv4_silu(ok, ok, ok, None, ok, 32, 64, 1, 32, 0, None) == -1
+    assert lib.miori_gemv4_silu(ok, ok, ok, ok, ok, 32, 96, 1, 64, 0, None) == -1
     assert lib.miori_rmsnorm(None, ok, ok, 1, 64, 1e-5, 0, None) == -1
     assert lib.miori_rmsnorm(ok, ok, ok, 0, 64, 1e-5, 0, None) == -1
     assert lib.miori_argmax(ok, 0, 0, ok, ok, None) == -1

@@ -122,3 +122,56 @@ def test_gemv_with_fused_rmsnorm(port, bits, N, K, M, group):
     unfused = (miori_b200.gemv4 if bits == 4 else miori_b200.gemv8)(
         q.to(DEV), s.to(DEV), b.to(DEV), xn_dev, group=group, flags=0x100000).cpu().numpy()
     assert_close(fused, unfused, rel_max=1e-3, what="fused vs unfused")
+
+
+TILED = 0x2000    # tuning flag: tiled TMA even where one slab of K fits the linear copies
+MMASYNC = 0x1000  # tuning flag: keep the unfused GEMV on the kernel the fused entry runs on
+
+
+@pytest.mark.parametrize("N,K,M,group,flags", [
+    (16384, 2048, 1, 64, 0), (16384, 2048, 2, 64, 0), (12288, 2048, 3, 64, 0), (4096, 2048, 4, 32, 0),
+    (2048, 2048, 8, 64, 0), (3072, 2048, 16, 64, 0), (1024, 1024, 16, 32, 0), (4096, 4096, 1, 64, 0),
+    (512, 8192, 2, 64, 0), (2048, 2048, 1, 64, TILED), (1024, 2048, 6, 32, TILED), (4096, 1024, 5, 32, 0),
+    (32, 2048, 1, 64, 0), (16, 512, 7, 64, 0), (6000 * 2, 1536, 4, 64, 0)])
+def test_gemv_with_silu_epilogue(port, N, K, M, group, flags):
+    """bf16(silu(gate) * up) out of the fused gate + up projection: bit for bit the unfused pair of
+    this library, and the oracle's GEMV followed by its silu_mul within one bf16 step (M <= 4, the
+    fp32-dequantization kernels) resp. the batched GEMV's tolerance."""
+    q, s, b = synth.make_weight(N, K, 4, group, seed=N + K + M)
+    x = synth.make_activation(M, K, seed=M)
+    dq, ds, db, dx = q.to(DEV), s.to(DEV), b.to(DEV), x.to(DEV)
+    fused = miori_b200.gemv4_silu(dq, ds, db, dx, group=group, flags=flags)
+    assert fused.shape == (M, N // 2) and fused.dtype == torch.bfloat16
+    y = miori_b200.gemv4(dq, ds, db, dx, group=group, flags=flags | MMASYNC)
+    h = N // 2
+    unfused = miori_b200.silu_mul(y[:, :h].contiguous(), y[:, h:].contiguous())
+    assert torch.equal(fused.view(torch.int16), unfused.view(torch.int16)), "fused and unfused differ"
+    want_y = port.gemv(4, u32(q), u16(s), u16(b), u16(x), group)
+    want = port.silu_mul(np.ascontiguousarray(want_y[:, :h]), np.ascontiguousarray(want_y[:, h:]))
+    got = fused.float().cpu().numpy()
+    ref = (want.astype(np.uint32) << 16).view(np.float32).reshape(got.shape)
+    if M <= 4:
+        # one bf16 step plus what the GEMV's fp32 sums (within 2e-5 of the largest output) may move a
+        # small product by; nearly all outputs equal bit for bit
+        assert (np.abs(got - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-3).all()
+        assert (u16(fused).reshape(-1) != want.reshape(-1)).mean() < 0.01
+    else:
+        assert_close(got, ref, rel_max=2e-2, what=f"gated gemv4 M={M}")
+    assert miori_b200.lib.miori_device_error_poll() == 0
+
+
+def test_gemv_with_silu_epilogue_refuses_what_it_cannot_take():
+    q, s, b = synth.make_weight(48, 2048, 4, 64, seed=1)
+    x = synth.make_activation(1, 2048, seed=1).to(DEV)
+    with pytest.raises(miori_b200.MioriError, match="multiple of 16"):
+        miori_b200.gemv4_silu(q[:40].contiguous().to(DEV), s[:40].contiguous().to(DEV), b[:40].contiguous().to(DEV), x,
+                              group=64)
+    # scale rows of 96 / 32 = 3 groups have no 16-byte pitch: outside the TMA kernel's range
+    q2, s2, b2 = synth.make_weight(32, 96, 4, 32, seed=2)
+    x2 = synth.make_activation(1, 96, seed=2).to(DEV)
+    with pytest.raises(miori_b200.MioriError, match="outside the fused kernel's range"):
+        miori_b200.gemv4_silu(q2.to(DEV), s2.to(DEV), b2.to(DEV), x2, group=32)
+    # more than 16 activation rows do not fit the kernel's staging area
+    x3 = synth.make_activation(17, 2048, seed=3).to(DEV)
+    with pytest.raises(miori_b200.MioriError, match="outside 1..16"):
+        miori_b200.gemv4_silu(q.to(DEV), s.to(DEV), b.to(DEV), x3, group=64)
