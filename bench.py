@@ -1006,6 +1006,39 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
                                  "how": "CUDA graphs of PDL launches; miori_gemv4 on w1 and on w3 then miori_silu_mul (three "
                                         "launches), miori_gemv4 on the fused weights then miori_silu_mul (two, one row), "
                                         "and miori_gemv4_silu (TMA + mma.sync kernel, gated epilogue)"}
+    # post_norm_add behind the o and w2 projections (M = 1): GEMV + norm kernel against the GEMV with the
+    # norm as its epilogue, over pools of distinct weights (> L2)
+    post = {}
+    for N, K in ((2048, 2048), (2048, 8192)):
+        npool = max(2, min(24, (300 << 20) // packed_bytes(N, K, 4, G)))
+        pool = [synth.make_weight(N, K, 4, G, seed=850 + i, device=dev) for i in range(npool)]
+        xg = synth.make_activation(1, K, seed=6, device=dev)
+        resid = torch.randn((1, N), device=dev)
+        gam = torch.ones(N, dtype=torch.bfloat16, device=dev)
+        v = torch.empty((1, N), device=dev)
+        o = torch.empty((1, N), device=dev)
+        counter = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def gemv_then_norm():
+            for q, s, b in pool:
+                miori_b200.gemv4(q, s, b, xg, group=G, flags=flags, out=v)
+                miori_b200.post_norm_add(resid, v, gam, 1e-5, flags=flags, out=o)
+
+        def norm_in_epilogue():
+            for q, s, b in pool:
+                miori_b200.gemv4_post_norm_add(q, s, b, xg, resid, gam, 1e-5, counter, group=G, flags=flags, out=o)
+        res = {}
+        for name, fn in (("gemv_then_post_norm_add_us", gemv_then_norm), ("fused_us", norm_in_epilogue)):
+            fn()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            res[name] = 1e3 * timed(g.replay, 10) / 10 / npool
+        post[f"N{N}_K{K}"] = res
+        del pool
+    ex["post_norm_add_fusion_m1"] = {"per_projection": post,
+                                     "how": "CUDA graphs of PDL launches; miori_gemv4 then miori_post_norm_add against "
+                                            "miori_gemv4_post_norm_add (the last CTA to finish normalises the rows)"}
     # config 3: prefill GEMM M=1024 on the bf16 cache + cache build.  Each shape runs over a
     # pool of distinct caches larger than L2 (weights come from HBM, as in a real prefill where
     # consecutive layers evict each other), one CUDA graph of PDL launches per shape.

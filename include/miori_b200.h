@@ -327,6 +327,18 @@ int miori_argmax(const void* v, uint32_t n, uint32_t flags, void* out_index, voi
  * shapes it does not take get MIORI_E_INVALID. */
 int miori_gemv4_silu(const void* q, const void* s, const void* b, const void* x, void* y, uint32_t N,
                      uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream);
+/* miori_gemv4 with post_norm_add (shaders/ops.metal:605-631) as its epilogue, for the o and w2
+ * projections of a decode step: out = residual + v * rsqrt(mean(v^2) + eps) * gamma over each
+ * output row v = W x; residual and out fp32 [M][N] (distinct), gamma bf16 [N], M <= 4.  Every CTA
+ * stores its rows of v into out; the one that finishes last runs the stand-alone kernel's row pass
+ * over out in place, so the result is bit for bit that of miori_gemv4 followed by
+ * miori_post_norm_add.  `counter` is one 32-bit word of device memory that is zero before the first
+ * launch; the kernel leaves it zero.  Launches that may run concurrently need counters of their
+ * own.  Shapes the TMA + mma.sync kernel does not take get MIORI_E_INVALID. */
+int miori_gemv4_post_norm_add(const void* q, const void* s, const void* b, const void* x,
+                              const void* residual, const void* gamma, float eps, void* counter,
+                              void* out, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                              uint32_t flags, void* stream);
 /* miori_gemv4 / miori_gemv8 with the RMSNorm of the activations fused into their staging:
  * y = W * bf16(rmsnorm(x)), x fp32 [M][K], gamma bf16 [K].  Saves the norm's launch and the
  * round trip of its output (the fusion the reference planned, docs/MILESTONES.md:87).  Runs on

@@ -19,6 +19,7 @@
 #pragma once
 #include "common.cuh"
 #include "gemv_mma.cuh"
+#include "norm.cuh"
 #include "peers.cuh"
 #include "tma_host.cuh"
 
@@ -273,8 +274,16 @@ __device__ __forceinline__ unsigned long long gtimer() {
 // the candidates meet in a 64-bit atomic maximum, and the CTA that finishes last exchanges this
 // rank's best with the peers (peers.cuh: peer_argmax_exchange), so the kernel ends with the winning
 // token on every rank and nothing else has crossed NVLink.
+// What the post-norm epilogue needs besides the GEMV's own arguments (null residual: off).
+struct PostNorm {
+    const float* residual = nullptr;   // x of post_norm_add, fp32 [M][N]
+    const uint16_t* gamma = nullptr;   // bf16 [N]
+    unsigned int* arrivals = nullptr;  // one zeroed word; the kernel leaves it zero
+    float eps = 0.0f;
+};
+
 template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR, bool ARGMAX = false,
-          bool GATED = false>
+          bool GATED = false, bool POSTNORM = false>
 __global__ void __launch_bounds__(THREADS, (NT == 1 && !ROOMY) ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_s,
@@ -283,8 +292,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
                 uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar,
                 const PeerArgs pa, uint32_t n_total, uint32_t row0, size_t y_off,
-                unsigned long long* __restrict__ best) {
+                unsigned long long* __restrict__ best, const PostNorm pn) {
     static_assert(!ARGMAX || SHARDED, "the arg-max epilogue lives in the sharded instantiation");
+    // POSTNORM: y = residual + v * rsqrt(mean(v^2) + eps) * gamma over each whole output row v of
+    // the GEMV (shaders/ops.metal:605-631).  Every CTA stores its part of v into y; the CTA that
+    // arrives last then runs the stand-alone kernel's row pass over y in place.
+    static_assert(!POSTNORM || (!OUT_BF16 && !SHARDED && !GATED), "the post-norm epilogue: fp32 out, one GPU");
     // GATED: the weight rows are a gate half [0, N/2) and an up half [N/2, N) (the fused w1/w3
     // projection); a tile is eight rows of each, so that after the tile's reduction one thread
     // pair holds gate and up of the same output, and y is bf16 [M][N/2] of silu(gate) * up.
@@ -818,7 +831,26 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
     }
-    if constexpr (ARGMAX) {  // every thread of the CTA gets here: no early exits above
+    if constexpr (POSTNORM) {  // every thread of the CTA gets here: no early exits above
+        __shared__ float pn_part[neighbors::NORM_THREADS / 32];
+        __shared__ uint32_t pn_last;
+        __threadfence();  // this thread's rows of v are visible before the CTA reports in
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            pn_last = atomicAdd(pn.arrivals, 1u) == gridDim.x - 1u ? 1u : 0u;
+            __threadfence();
+        }
+        __syncthreads();
+        if (pn_last && threadIdx.x < (uint32_t)neighbors::NORM_THREADS) {
+            float* out = reinterpret_cast<float*>(y);
+            for (uint32_t m = 0; m < M; ++m) {
+                const size_t at = (size_t)m * N;
+                neighbors::post_norm_add_row<9, true>(pn.residual + at, out + at, pn.gamma, out + at, N, pn.eps, pn_part);
+                neighbors::norm_sync<9>();  // pn_part is reused by the next row
+            }
+            if (threadIdx.x == 0) *pn.arrivals = 0u;  // ready for the next launch
+        }
+    } else if constexpr (ARGMAX) {  // every thread of the CTA gets here: no early exits above
         unsigned long long k = my_best;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -878,6 +910,8 @@ struct Shard {
     // gated epilogue (4-bit weights, one GPU): rows [0, N/2) are the gate and [N/2, N) the up
     // projection, y is bf16 [M][N/2] of silu(gate) * up
     bool gated = false;
+    // post-norm epilogue (4-bit weights, fp32 out, up to four rows, one GPU); residual null: off
+    PostNorm post;
 };
 
 // Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
@@ -955,10 +989,10 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     if (rc) return rc;
     const uint8_t* ql = linear ? reinterpret_cast<const uint8_t*>(q) : nullptr;
     cudaError_t e = cudaSuccess;
-#define MIORI_TMA_LAUNCH(OB, SH, AM, GT)                                                         \
+#define MIORI_TMA_LAUNCH(OB, SH, AM, GT, PN)                                                     \
     do {                                                                                         \
-        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM, GT>      \
-                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM, GT>;       \
+        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM, GT, PN>  \
+                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM, GT, PN>;   \
         e = cudaSuccess;                                                                         \
         if (smem_l > 48 * 1024)                                                                  \
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_l); \
@@ -966,7 +1000,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
             e = launch(kern, dim3(grid), dim3(THREADS), smem_l, stream, pdl, tq, ts, tb, ql,     \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
                        reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
-                       sh.pa, placed ? sh.n_total : N, placed ? sh.row0 : 0u, sh.y_off, sh.best);  \
+                       sh.pa, placed ? sh.n_total : N, placed ? sh.row0 : 0u, sh.y_off, sh.best, sh.post); \
     } while (0)
     const bool sharded = sh.pa.world > 1;
     constexpr bool can_argmax = EXACT && NT == 1 && !PAIR;  // the one- and two-row kernels
@@ -978,20 +1012,28 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     const size_t smem_l = plan.pad ? std::max<size_t>(smem, 120 * 1024) : smem;
     if (sh.gated && (BITS != 4 || sharded || argmax || N % 16 != 0))
         return fail(MIORI_E_INVALID, "the gated epilogue takes 4-bit weights with N a multiple of 16 on one GPU");
+    const bool postnorm = sh.post.residual != nullptr;
+    if (postnorm && (BITS != 4 || !EXACT || sharded || argmax || sh.gated || (flags & MIORI_OUT_BF16)))
+        return fail(MIORI_E_INVALID, "the post-norm epilogue takes 4-bit weights, up to four rows, fp32 out, one GPU");
     if constexpr (can_argmax) {
         if (argmax) {
-            if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true, true, true, false);
-            else MIORI_TMA_LAUNCH(false, true, true, false);
+            if (flags & MIORI_OUT_BF16) MIORI_TMA_LAUNCH(true, true, true, false, false);
+            else MIORI_TMA_LAUNCH(false, true, true, false, false);
         }
     }
     if constexpr (BITS == 4) {
-        if (sh.gated) MIORI_TMA_LAUNCH(true, false, false, true);
+        if (sh.gated) MIORI_TMA_LAUNCH(true, false, false, true, false);
     }
-    if (!argmax && !sh.gated) {
+    if constexpr (BITS == 4 && EXACT) {
+        if (postnorm) MIORI_TMA_LAUNCH(false, false, false, false, true);
+    }
+    if (!argmax && !sh.gated && !postnorm) {
         if (flags & MIORI_OUT_BF16) {
-            if (sharded) MIORI_TMA_LAUNCH(true, true, false, false); else MIORI_TMA_LAUNCH(true, false, false, false);
+            if (sharded) MIORI_TMA_LAUNCH(true, true, false, false, false);
+            else MIORI_TMA_LAUNCH(true, false, false, false, false);
         } else {
-            if (sharded) MIORI_TMA_LAUNCH(false, true, false, false); else MIORI_TMA_LAUNCH(false, false, false, false);
+            if (sharded) MIORI_TMA_LAUNCH(false, true, false, false, false);
+            else MIORI_TMA_LAUNCH(false, false, false, false, false);
         }
     }
 #undef MIORI_TMA_LAUNCH

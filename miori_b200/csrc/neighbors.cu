@@ -7,29 +7,10 @@
 //   post_norm_add  shaders/ops.metal:605-631  out = x + src * rsqrt(mean(src^2) + eps) * w
 //   embed8         shaders/ops.metal:170-197  out[t][k] = bf16(code * scale + bias) of row tokens[t]
 #include "common.cuh"
+#include "norm.cuh"
 
 namespace miori_b200 {
 namespace neighbors {
-
-constexpr int NORM_THREADS = 256;
-
-// Sum of squares of a row over the CTA, in a fixed order: every thread adds its strided elements,
-// warps reduce by shuffles, warp 0 adds the eight warp sums.
-__device__ __forceinline__ float row_sum_squares(const float* __restrict__ row, uint32_t n, float* part) {
-    float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < n; i += NORM_THREADS) {
-        const float v = row[i];
-        ss = __fmaf_rn(v, v, ss);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-    if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-#pragma unroll
-    for (int i = 0; i < NORM_THREADS / 32; ++i) tot += part[i];
-    return tot;
-}
 
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(const float* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
@@ -38,7 +19,7 @@ rmsnorm_kernel(const float* __restrict__ x, const uint16_t* __restrict__ w, uint
     pdl_launch_dependents();
     pdl_wait_prior();
     const float* row = x + (size_t)blockIdx.x * n;
-    const float inv = rsqrtf(row_sum_squares(row, n, part) / (float)n + eps);
+    const float inv = rsqrtf(row_sum_squares<0, false>(row, n, part) / (float)n + eps);
     for (uint32_t i = threadIdx.x; i < n; i += NORM_THREADS)
         y[(size_t)blockIdx.x * n + i] = (uint16_t)float_to_bf16_bits(row[i] * inv * bf16_bits_to_float(w[i]));
 }
@@ -49,12 +30,8 @@ post_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ src,
     __shared__ float part[NORM_THREADS / 32];
     pdl_launch_dependents();
     pdl_wait_prior();
-    const float* row = src + (size_t)blockIdx.x * n;
-    const float inv = rsqrtf(row_sum_squares(row, n, part) / (float)n + eps);
-    for (uint32_t i = threadIdx.x; i < n; i += NORM_THREADS) {
-        const size_t at = (size_t)blockIdx.x * n + i;
-        out[at] = x[at] + row[i] * inv * bf16_bits_to_float(w[i]);
-    }
+    const size_t at = (size_t)blockIdx.x * n;
+    post_norm_add_row<0, false>(x + at, src + at, w, out + at, n, eps, part);
 }
 
 __global__ void __launch_bounds__(256)

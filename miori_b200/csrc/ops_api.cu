@@ -119,6 +119,30 @@ MIORI_API int miori_gemv4_silu(const void* q, const void* s, const void* b, cons
     return rc;
 }
 
+MIORI_API int miori_gemv4_post_norm_add(const void* q, const void* s, const void* b, const void* x,
+                                        const void* residual, const void* gamma, float eps, void* counter,
+                                        void* out, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                                        uint32_t flags, void* stream) {
+    const char* op = "miori_gemv4_post_norm_add";
+    int rc = check_quant_args(op, q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!x || !residual || !gamma || !counter || !out) return fail(MIORI_E_INVALID, "%s: null pointer", op);
+    if (M == 0 || M > 4) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..4", op, M);
+    if (!aligned16(x)) return fail(MIORI_E_INVALID, "%s: x must be 16-byte aligned", op);
+    if (flags & MIORI_OUT_BF16) return fail(MIORI_E_INVALID, "%s: the output is fp32", op);
+    if (out == residual) return fail(MIORI_E_INVALID, "%s: out must not be the residual", op);
+    gemvtma::Shard sh;
+    sh.post.residual = static_cast<const float*>(residual);
+    sh.post.gamma = static_cast<const uint16_t*>(gamma);
+    sh.post.arrivals = static_cast<unsigned int*>(counter);
+    sh.post.eps = eps;
+    rc = gemvtma::try_launch<4>(q, s, b, x, out, N, K, M, group, flags, (cudaStream_t)stream, sh);
+    if (rc == 1)
+        return fail(MIORI_E_INVALID, "%s: shape N=%u K=%u M=%u group=%u is outside the fused kernel's range "
+                    "(run the plain GEMV and miori_post_norm_add instead)", op, N, K, M, group);
+    return rc;
+}
+
 MIORI_API int miori_gemv4_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
                                   float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
                                   uint32_t flags, void* stream) {

@@ -229,3 +229,22 @@ def gemv4_silu(q, s, b, x, group=32, flags=0, out=None):
     check(lib.miori_gemv4_silu(q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), y.data_ptr(), N, K, M,
                                group, flags, _stream()))
     return y
+
+
+def gemv4_post_norm_add(q, s, b, x, residual, gamma, eps, counter, group=32, flags=0, out=None):
+    """residual + v * rsqrt(mean(v^2) + eps) * gamma for v = gemv4(x), fp32 [M][N], M <= 4: gemv4 with
+    post_norm_add as its epilogue.  `counter`: a zeroed int32 tensor of one element, left zero."""
+    _need_cuda(q, s, b, x, residual, gamma, counter)
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    M, K = x.shape
+    N = q.shape[0]
+    if q.shape[1] * 8 != K:
+        raise ValueError(f"q has {q.shape[1]} words per row, expected {K // 8}")
+    if residual.dtype != torch.float32 or residual.numel() != M * N:
+        raise ValueError("residual: fp32 [M][N] expected")
+    o = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    check(lib.miori_gemv4_post_norm_add(q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), residual.data_ptr(),
+                                        gamma.data_ptr(), float(eps), counter.data_ptr(), o.data_ptr(), N, K, M,
+                                        group, flags, _stream()))
+    return o

@@ -175,3 +175,44 @@ def test_gemv_with_silu_epilogue_refuses_what_it_cannot_take():
     x3 = synth.make_activation(17, 2048, seed=3).to(DEV)
     with pytest.raises(miori_b200.MioriError, match="outside 1..16"):
         miori_b200.gemv4_silu(q.to(DEV), s.to(DEV), b.to(DEV), x3, group=64)
+
+
+@pytest.mark.parametrize("N,K,M,group,flags", [
+    (2048, 2048, 1, 64, 0), (2048, 8192, 1, 64, 0), (2048, 2048, 2, 32, 0), (2048, 2048, 3, 64, 0),
+    (2048, 8192, 4, 64, 0), (1000, 2048, 4, 32, 0), (2048, 2048, 1, 64, TILED), (16, 512, 2, 64, 0),
+    (5120, 4096, 1, 64, 0)])
+def test_gemv_with_post_norm_add_epilogue(port, N, K, M, group, flags):
+    """residual + v * rsqrt(mean(v^2) + eps) * gamma with v the GEMV's output row: bit for bit the
+    unfused pair of this library, close to the oracle's pair, repeatable, and the arrival counter is
+    left at zero."""
+    q, s, b = synth.make_weight(N, K, 4, group, seed=N + K + M)
+    x = synth.make_activation(M, K, seed=M)
+    g = torch.Generator().manual_seed(N + M)
+    res = torch.randn((M, N), generator=g)
+    w = (torch.randn(N, generator=g) * 0.1 + 1.0).to(torch.bfloat16)
+    dq, ds, db, dx, dres, dw = q.to(DEV), s.to(DEV), b.to(DEV), x.to(DEV), res.to(DEV), w.to(DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fused = miori_b200.gemv4_post_norm_add(dq, ds, db, dx, dres, dw, 1e-5, counter, group=group, flags=flags)
+    again = miori_b200.gemv4_post_norm_add(dq, ds, db, dx, dres, dw, 1e-5, counter, group=group, flags=flags)
+    assert int(counter.item()) == 0
+    v = miori_b200.gemv4(dq, ds, db, dx, group=group, flags=flags | MMASYNC)
+    unfused = miori_b200.post_norm_add(dres, v, dw, 1e-5)
+    assert torch.equal(fused, unfused), "fused and unfused differ"
+    assert torch.equal(fused, again), "second launch differs"
+    want_v = port.gemv(4, u32(q), u16(s), u16(b), u16(x), group)
+    want = port.post_norm_add(res.numpy(), want_v.astype(np.float32), u16(w), 1e-5)
+    assert_close(fused.cpu().numpy(), want, rel_max=1e-4, what=f"post-norm gemv4 M={M}")
+    assert miori_b200.lib.miori_device_error_poll() == 0
+
+
+def test_gemv_with_post_norm_add_epilogue_refuses_what_it_cannot_take():
+    q, s, b = synth.make_weight(64, 2048, 4, 64, seed=1)
+    x = synth.make_activation(5, 2048, seed=1).to(DEV)
+    res = torch.zeros((5, 64), device=DEV)
+    w = torch.ones(64, dtype=torch.bfloat16, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(miori_b200.MioriError, match="outside 1..4"):
+        miori_b200.gemv4_post_norm_add(q.to(DEV), s.to(DEV), b.to(DEV), x, res, w, 1e-5, counter, group=64)
+    with pytest.raises(miori_b200.MioriError, match="must not be the residual"):
+        miori_b200.gemv4_post_norm_add(q.to(DEV), s.to(DEV), b.to(DEV), x[:1].contiguous(), res[:1], w, 1e-5,
+                                       counter, group=64, out=res[:1])
