@@ -1039,6 +1039,53 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
     ex["post_norm_add_fusion_m1"] = {"per_projection": post,
                                      "how": "CUDA graphs of PDL launches; miori_gemv4 then miori_post_norm_add against "
                                             "miori_gemv4_post_norm_add (the last CTA to finish normalises the rows)"}
+    # One decode layer at M = 1 with its neighbours (attention left out: o reads a fixed vector), 24
+    # layers of distinct weights in one graph: the reference's ten launches per layer against the eight
+    # that the measured fusions leave (SiLU x up in the gate + up GEMV; the norms stay kernels)
+    H, QKV, FF = 2048, 3072, 8192
+    layers = [[synth.make_weight(n, k, 4, G, seed=9000 + 4 * i + j, device=dev)
+               for j, (n, k) in enumerate(((QKV, H), (H, H), (2 * FF, H), (H, FF)))] for i in range(24)]
+    hid = torch.randn((1, H), device=dev)
+    gam = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    xn = torch.empty((1, H), dtype=torch.bfloat16, device=dev)
+    attn = synth.make_activation(1, H, seed=8, device=dev)
+    qkv = torch.empty((1, QKV), device=dev)
+    proj = torch.empty((1, H), device=dev)
+    h2 = torch.empty((1, H), device=dev)
+    h3 = torch.empty((1, H), device=dev)
+    gate = torch.empty((1, FF), device=dev)
+    up = torch.empty((1, FF), device=dev)
+    act = torch.empty((1, FF), dtype=torch.bfloat16, device=dev)
+
+    def layer(wq, wo, wgu, wd, fuse):
+        miori_b200.rmsnorm(hid, gam, 1e-5, flags=flags, out=xn)
+        miori_b200.gemv4(*wq, xn, group=G, flags=flags, out=qkv)
+        miori_b200.gemv4(*wo, attn, group=G, flags=flags, out=proj)
+        miori_b200.post_norm_add(hid, proj, gam, 1e-5, flags=flags, out=h2)
+        miori_b200.rmsnorm(h2, gam, 1e-5, flags=flags, out=xn)
+        if fuse:
+            miori_b200.gemv4_silu(*wgu, xn, group=G, flags=flags, out=act)
+        else:
+            q, s, b = wgu
+            miori_b200.gemv4(q[:FF], s[:FF], b[:FF], xn, group=G, flags=flags, out=gate)
+            miori_b200.gemv4(q[FF:], s[FF:], b[FF:], xn, group=G, flags=flags, out=up)
+            miori_b200.silu_mul(gate, up, flags=flags, out=act)
+        miori_b200.gemv4(*wd, act, group=G, flags=flags, out=proj)
+        miori_b200.post_norm_add(h2, proj, gam, 1e-5, flags=flags, out=h3)
+    res = {}
+    for name, fuse in (("ten_launches_us", False), ("eight_launches_us", True)):
+        def run():
+            for ws in layers:
+                layer(*ws, fuse)
+        run()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        res[name] = 1e3 * timed(g.replay, 10) / 10 / len(layers)
+    del layers
+    ex["decode_layer_m1_with_neighbours"] = dict(res, how="us per layer; rmsnorm, qkv, o, post_norm_add, rmsnorm, w1, w3, "
+                                                 "silu_mul, w2, post_norm_add against the same with miori_gemv4_silu "
+                                                 "in place of w1, w3, silu_mul; CUDA graph of PDL launches")
     # config 3: prefill GEMM M=1024 on the bf16 cache + cache build.  Each shape runs over a
     # pool of distinct caches larger than L2 (weights come from HBM, as in a real prefill where
     # consecutive layers evict each other), one CUDA graph of PDL launches per shape.
