@@ -949,8 +949,13 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
         def one_kernel():
             for q, s, b in pool:
                 miori_b200.gemv4_rmsnorm(q, s, b, xf, gam, 1e-5, group=G, flags=flags, out=y)
+
+        def one_kernel_tcgen05():
+            for q, s, b in pool:
+                miori_b200.gemv4_rmsnorm(q, s, b, xf, gam, 1e-5, group=G, flags=flags | 0x100000, out=y)
         res = {}
-        for name, fn in (("norm_then_gemv_us", two_kernels), ("fused_us", one_kernel)):
+        for name, fn in (("norm_then_gemv_us", two_kernels), ("fused_us", one_kernel),
+                         ("fused_tcgen05_us", one_kernel_tcgen05)):
             fn()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
@@ -962,7 +967,8 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
                                "layer_norm_then_gemv_us": sum(v["norm_then_gemv_us"] for v in fused.values()),
                                "layer_fused_us": sum(v["fused_us"] for v in fused.values()),
                                "how": "CUDA graphs of PDL launches; the unfused pair is the default GEMV after "
-                                      "miori_rmsnorm, the fused one miori_gemv4_rmsnorm (tcgen05 kernel)"}
+                                      "miori_rmsnorm, the fused one miori_gemv4_rmsnorm (by default the TMA + mma.sync "
+                                      "kernel with the norm in its staging pass; the tcgen05 kernel when forced)"}
     # SiLU x up behind the fused gate + up projection (2048 -> 2 x 8192): GEMV + activation kernel
     # against the GEMV with the activation as its epilogue, over a pool of distinct weights (> L2)
     N, K = 16384, 2048
@@ -1040,8 +1046,9 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
                                      "how": "CUDA graphs of PDL launches; miori_gemv4 then miori_post_norm_add against "
                                             "miori_gemv4_post_norm_add (the last CTA to finish normalises the rows)"}
     # One decode layer at M = 1 with its neighbours (attention left out: o reads a fixed vector), 24
-    # layers of distinct weights in one graph: the reference's ten launches per layer against the eight
-    # that the measured fusions leave (SiLU x up in the gate + up GEMV; the norms stay kernels)
+    # layers of distinct weights in one graph: the reference's ten launches per layer, eight with SiLU x up
+    # in the gate + up GEMV, seven with qkv's norm in its GEMV's staging, six with the other input norm in
+    # front of the gated GEMV too (the post-norms stay kernels: fused they measured slower)
     H, QKV, FF = 2048, 3072, 8192
     layers = [[synth.make_weight(n, k, 4, G, seed=9000 + 4 * i + j, device=dev)
                for j, (n, k) in enumerate(((QKV, H), (H, H), (2 * FF, H), (H, FF)))] for i in range(24)]
@@ -1058,12 +1065,20 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
     act = torch.empty((1, FF), dtype=torch.bfloat16, device=dev)
 
     def layer(wq, wo, wgu, wd, fuse):
-        miori_b200.rmsnorm(hid, gam, 1e-5, flags=flags, out=xn)
-        miori_b200.gemv4(*wq, xn, group=G, flags=flags, out=qkv)
+        if fuse >= 2:
+            miori_b200.gemv4_rmsnorm(*wq, hid, gam, 1e-5, group=G, flags=flags, out=qkv)
+        else:
+            miori_b200.rmsnorm(hid, gam, 1e-5, flags=flags, out=xn)
+            miori_b200.gemv4(*wq, xn, group=G, flags=flags, out=qkv)
         miori_b200.gemv4(*wo, attn, group=G, flags=flags, out=proj)
         miori_b200.post_norm_add(hid, proj, gam, 1e-5, flags=flags, out=h2)
-        miori_b200.rmsnorm(h2, gam, 1e-5, flags=flags, out=xn)
-        if fuse:
+        if fuse == 3:
+            miori_b200.gemv4_rmsnorm_silu(*wgu, h2, gam, 1e-5, group=G, flags=flags, out=act)
+        else:
+            miori_b200.rmsnorm(h2, gam, 1e-5, flags=flags, out=xn)
+        if fuse == 3:
+            pass
+        elif fuse:
             miori_b200.gemv4_silu(*wgu, xn, group=G, flags=flags, out=act)
         else:
             q, s, b = wgu
@@ -1073,7 +1088,7 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
         miori_b200.gemv4(*wd, act, group=G, flags=flags, out=proj)
         miori_b200.post_norm_add(h2, proj, gam, 1e-5, flags=flags, out=h3)
     res = {}
-    for name, fuse in (("ten_launches_us", False), ("eight_launches_us", True)):
+    for name, fuse in (("ten_launches_us", 0), ("eight_launches_us", 1), ("seven_launches_us", 2), ("six_launches_us", 3)):
         def run():
             for ws in layers:
                 layer(*ws, fuse)
@@ -1084,8 +1099,10 @@ def extras(torch, miori_b200, synth, dev, G, peaks, timed):
         res[name] = 1e3 * timed(g.replay, 10) / 10 / len(layers)
     del layers
     ex["decode_layer_m1_with_neighbours"] = dict(res, how="us per layer; rmsnorm, qkv, o, post_norm_add, rmsnorm, w1, w3, "
-                                                 "silu_mul, w2, post_norm_add against the same with miori_gemv4_silu "
-                                                 "in place of w1, w3, silu_mul; CUDA graph of PDL launches")
+                                                 "silu_mul, w2, post_norm_add; with miori_gemv4_silu in place of w1, w3, "
+                                                 "silu_mul (eight); with miori_gemv4_rmsnorm for qkv as well (seven); with "
+                                                 "miori_gemv4_rmsnorm_silu for the gate + up projection too (six); "
+                                                 "CUDA graph of PDL launches")
     # config 3: prefill GEMM M=1024 on the bf16 cache + cache build.  Each shape runs over a
     # pool of distinct caches larger than L2 (weights come from HBM, as in a real prefill where
     # consecutive layers evict each other), one CUDA graph of PDL launches per shape.

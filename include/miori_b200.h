@@ -327,6 +327,11 @@ int miori_argmax(const void* v, uint32_t n, uint32_t flags, void* out_index, voi
  * shapes it does not take get MIORI_E_INVALID. */
 int miori_gemv4_silu(const void* q, const void* s, const void* b, const void* x, void* y, uint32_t N,
                      uint32_t K, uint32_t M, uint32_t group, uint32_t flags, void* stream);
+/* The gate + up projection with both neighbours: y = bf16(silu(g) * u) of W * bf16(rmsnorm(x)), x fp32
+ * [M][K], gamma bf16 [K], y bf16 [M][N/2]; M <= 4.  One launch for rmsnorm, w1, w3 and silu_mul. */
+int miori_gemv4_rmsnorm_silu(const void* q, const void* s, const void* b, const void* x, const void* gamma,
+                             float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
+                             uint32_t flags, void* stream);
 /* miori_gemv4 with post_norm_add (shaders/ops.metal:605-631) as its epilogue, for the o and w2
  * projections of a decode step: out = residual + v * rsqrt(mean(v^2) + eps) * gamma over each
  * output row v = W x; residual and out fp32 [M][N] (distinct), gamma bf16 [N], M <= 4.  Every CTA
@@ -341,8 +346,12 @@ int miori_gemv4_post_norm_add(const void* q, const void* s, const void* b, const
                               uint32_t flags, void* stream);
 /* miori_gemv4 / miori_gemv8 with the RMSNorm of the activations fused into their staging:
  * y = W * bf16(rmsnorm(x)), x fp32 [M][K], gamma bf16 [K].  Saves the norm's launch and the
- * round trip of its output (the fusion the reference planned, docs/MILESTONES.md:87).  Runs on
- * the tcgen05 kernel; shapes it does not take get MIORI_E_INVALID. */
+ * round trip of its output (the fusion the reference planned, docs/MILESTONES.md:87).  4-bit
+ * weights with up to four rows of K <= 2048 and fp32 out run on the TMA + mma.sync kernel (every CTA
+ * sums the rows' squares for itself, then normalises while it stages), everything else on the tcgen05
+ * kernel; shapes
+ * neither takes get MIORI_E_INVALID.  The result is the unfused pair's up to the fp32 order of the sum
+ * of squares. */
 int miori_gemv4_rmsnorm(const void* q, const void* s, const void* b, const void* x, const void* gamma,
                         float eps, void* y, uint32_t N, uint32_t K, uint32_t M, uint32_t group,
                         uint32_t flags, void* stream);

@@ -13,7 +13,7 @@ import importlib
 _OPS = ("gemv4", "gemv8", "dequant4_rowmajor", "dequant8_rowmajor", "dequant4_cache",
         "cache_to_rowmajor", "gemm_bf16_cache", "gemv_bf16_cache", "gemm_workspace", "gemm_bf16_strided", "linear4",
         "rmsnorm", "post_norm_add", "silu_mul", "embed8", "argmax", "gemv4_rmsnorm", "gemv8_rmsnorm",
-        "gemv4_silu", "gemv4_post_norm_add")
+        "gemv4_silu", "gemv4_post_norm_add", "gemv4_rmsnorm_silu")
 _LIB = ("lib", "check", "MioriError", "OUT_F32", "OUT_BF16", "LAUNCH_PDL", "GEMV_EXACT")
 
 __all__ = list(_OPS + _LIB)

@@ -78,6 +78,7 @@ _SIGS = {
     "miori_argmax": (_i, [_p, _u32, _u32, _p, _p, _p]),
     "miori_gemv4_silu": (_i, [_p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_gemv4_post_norm_add": (_i, [_p, _p, _p, _p, _p, _p, C.c_float, _p, _p, _u32, _u32, _u32, _u32, _u32, _p]),
+    "miori_gemv4_rmsnorm_silu": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_gemv4_rmsnorm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_gemv8_rmsnorm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _u32, _u32, _u32, _u32, _u32, _p]),
     "miori_device_error_poll": (_i, []),

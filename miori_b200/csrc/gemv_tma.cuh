@@ -97,11 +97,13 @@ __device__ __forceinline__ uint32_t x_unit(uint32_t step, uint32_t t, uint32_t w
 // Stage x for the MMA B operand: permuted to the k order of the A fragments (8-bit codes: as
 // fp16 scaled by `mul`), laid out by x_unit(); for EXACT also the fp32 sum of x over every chunk
 // (PAIR: over every pair of chunks, i.e. every 64-weight group).
-template <int BITS, bool EXACT, int MP, bool PAIR>
+// `ld8(m, u)` returns the eight bf16 activations 8u .. 8u+7 of row m (4-bit codes; the plain
+// loader reads x, the norm-fused one normalises fp32 activations on the fly).
+template <int BITS, bool EXACT, int MP, bool PAIR, class LD>
 __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, uint4* xs,
                                                float* xsum, uint32_t M, uint32_t K,
                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr,
-                                               const float* mul_rows) {
+                                               const float* mul_rows, LD ld8) {
     constexpr int CW = 128 / BITS, KU = BITS == 4 ? 8 : 4;
     const uint32_t upr = steps_p * 16u;  // logical units per row
     for (uint32_t i = threadIdx.x; i < (uint32_t)MP * upr; i += THREADS) {
@@ -109,7 +111,7 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
         uint4 o = make_uint4(0u, 0u, 0u, 0u);
         if (m < M && u * KU < K) {
             if (BITS == 4) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
+                const uint4 v = ld8(m, u);
                 o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0,x4)
                 o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1,x5)
                 o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
@@ -138,7 +140,7 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
                 const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)c0 * CW);
 #pragma unroll
                 for (int j = 0; j < (PAIR ? 2 : 1) * CW / 8; ++j) {
-                    const uint4 v = __ldg(xp + j);
+                    const uint4 v = BITS == 4 ? ld8(m, c0 * (CW / 8) + j) : __ldg(xp + j);
                     if (BITS == 4) {
                         sum += bf16lo(v.x); sum += bf16hi(v.x); sum += bf16lo(v.y); sum += bf16hi(v.y);
                         sum += bf16lo(v.z); sum += bf16hi(v.z); sum += bf16lo(v.w); sum += bf16hi(v.w);
@@ -161,10 +163,9 @@ __device__ __forceinline__ void stage_x_padded(const uint16_t* __restrict__ x, u
 // before either is used, so that a long row (K = 8192: four units per thread) costs two load
 // latencies, not four.  Whole warps iterate (THREADS and the units per row are multiples of 32
 // resp. 16, so lane groups never straddle a chunk).
-template <int BITS, bool EXACT, int MP, bool PAIR>
-__device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, uint4* xs,
-                                                float* xsum, uint32_t M, uint32_t K,
-                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
+template <int BITS, bool EXACT, int MP, bool PAIR, class LD>
+__device__ __forceinline__ void stage_x_onepass(uint4* xs, float* xsum, uint32_t M, uint32_t K,
+                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr, LD ld8) {
     static_assert(BITS == 4, "one-pass staging exists for 4-bit codes only (8-bit x is staged as scaled fp16)");
     static_assert(MP <= 4, "row index by comparison");
     constexpr int KU = 8;
@@ -181,7 +182,7 @@ __device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, 
             u[h] = i[h] - m[h] * upr;
             live[h] = i[h] < total && m[h] < M && u[h] * KU < K;
             v[h] = make_uint4(0u, 0u, 0u, 0u);
-            if (live[h]) v[h] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m[h] * K) + u[h]);
+            if (live[h]) v[h] = ld8(m[h], u[h]);
         }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -210,10 +211,9 @@ __device__ __forceinline__ void stage_x_onepass(const uint16_t* __restrict__ x, 
 // one load latency instead of two.  Whole warps iterate (THREADS and the units per row are
 // multiples of 32 resp. 16, so lane groups never straddle a chunk).  For long rows the two-pass
 // version above is faster: its loads are independent across iterations.
-template <int BITS, bool EXACT, int MP, bool PAIR>
-__device__ __forceinline__ void stage_x_onepass_wide(const uint16_t* __restrict__ x, uint4* xs,
-                                                float* xsum, uint32_t M, uint32_t K,
-                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr) {
+template <int BITS, bool EXACT, int MP, bool PAIR, class LD>
+__device__ __forceinline__ void stage_x_onepass_wide(uint4* xs, float* xsum, uint32_t M, uint32_t K,
+                                                uint32_t steps_p, uint32_t pitch, uint32_t cpr, LD ld8) {
     static_assert(BITS == 4, "one-pass staging exists for 4-bit codes only (8-bit x is staged as scaled fp16)");
     constexpr int KU = 8;
     const uint32_t upr = steps_p * 16u;  // logical units per row
@@ -224,7 +224,7 @@ __device__ __forceinline__ void stage_x_onepass_wide(const uint16_t* __restrict_
         uint4 o = make_uint4(0u, 0u, 0u, 0u);
         float sum = 0.0f;
         if (i < total && m < M && u * KU < K) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
+            const uint4 v = ld8(m, u);
             o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0,x4)
             o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1,x5)
             o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2,x6)
@@ -269,11 +269,6 @@ __device__ __forceinline__ unsigned long long gtimer() {
 #define TMA_MARK(i) do { } while (0)
 #endif
 
-// ARGMAX (with SHARDED, one activation row): the head of a greedy decode step.  The rows go to this
-// rank's y only -- no packets -- and every thread tracks the best (value, index) of what it stores;
-// the candidates meet in a 64-bit atomic maximum, and the CTA that finishes last exchanges this
-// rank's best with the peers (peers.cuh: peer_argmax_exchange), so the kernel ends with the winning
-// token on every rank and nothing else has crossed NVLink.
 // What the post-norm epilogue needs besides the GEMV's own arguments (null residual: off).
 struct PostNorm {
     const float* residual = nullptr;   // x of post_norm_add, fp32 [M][N]
@@ -282,8 +277,19 @@ struct PostNorm {
     float eps = 0.0f;
 };
 
+// What the norm prologue needs (null gamma: off): x then points at fp32 activations.
+struct PreNorm {
+    const uint16_t* gamma = nullptr;  // bf16 [K]
+    float eps = 0.0f;
+};
+
+// ARGMAX (with SHARDED, one activation row): the head of a greedy decode step.  The rows go to this
+// rank's y only -- no packets -- and every thread tracks the best (value, index) of what it stores;
+// the candidates meet in a 64-bit atomic maximum, and the CTA that finishes last exchanges this
+// rank's best with the peers (peers.cuh: peer_argmax_exchange), so the kernel ends with the winning
+// token on every rank and nothing else has crossed NVLink.
 template <int BITS, bool EXACT, int NT, bool OUT_BF16, bool SHARDED, bool ROOMY, bool PAIR, bool ARGMAX = false,
-          bool GATED = false, bool POSTNORM = false>
+          bool GATED = false, bool POSTNORM = false, bool NORMED = false>
 __global__ void __launch_bounds__(THREADS, (NT == 1 && !ROOMY) ? 2 : 1)
 gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_s,
@@ -292,12 +298,15 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t N, uint32_t K,
                 uint32_t M, uint32_t gshift, uint32_t ngrp, uint32_t nsg, uint32_t kpar,
                 const PeerArgs pa, uint32_t n_total, uint32_t row0, size_t y_off,
-                unsigned long long* __restrict__ best, const PostNorm pn) {
+                unsigned long long* __restrict__ best, const PostNorm pn, const PreNorm pre) {
     static_assert(!ARGMAX || SHARDED, "the arg-max epilogue lives in the sharded instantiation");
     // POSTNORM: y = residual + v * rsqrt(mean(v^2) + eps) * gamma over each whole output row v of
     // the GEMV (shaders/ops.metal:605-631).  Every CTA stores its part of v into y; the CTA that
     // arrives last then runs the stand-alone kernel's row pass over y in place.
     static_assert(!POSTNORM || (!OUT_BF16 && !SHARDED && !GATED), "the post-norm epilogue: fp32 out, one GPU");
+    // NORMED: x points at fp32 activations; the staging pass stages bf16(x * rsqrt(mean(x^2) + eps) *
+    // gamma) (shaders/ops.metal:86-115), each CTA computing the rows' sums of squares for itself.
+    static_assert(!NORMED || (BITS == 4 && EXACT && !SHARDED && !POSTNORM), "the norm prologue: 4-bit, up to four rows, one GPU");
     // GATED: the weight rows are a gate half [0, N/2) and an up half [N/2, N) (the fused w1/w3
     // projection); a tile is eight rows of each, so that after the tile's reduction one thread
     // pair holds gate and up of the same output, and y is bf16 [M][N/2] of silu(gate) * up.
@@ -528,19 +537,67 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         __syncthreads();
     }
+    __shared__ float nm_part[NORMED ? 4 * (WARPS + 1) : 1];
+    __shared__ float nm_inv[4];
+    if constexpr (NORMED) {
+        // sums of squares of the (at most four) rows: all loads in flight together, warps reduce by
+        // shuffles, one thread per row adds the warp sums in order
+        static_assert(MP <= 4, "rows of the norm prologue");
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const uint32_t qpr = K >> 2;  // float4 pieces per row (K is a multiple of 32)
+        float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t i = threadIdx.x; i < qpr; i += THREADS) {
+#pragma unroll
+            for (uint32_t m = 0; m < 4u; ++m) {
+                if (m < M) {
+                    const float4 v = __ldg(x4 + (size_t)m * qpr + i);
+                    ss[m] = __fmaf_rn(v.w, v.w, __fmaf_rn(v.z, v.z, __fmaf_rn(v.y, v.y, __fmaf_rn(v.x, v.x, ss[m]))));
+                }
+            }
+        }
+#pragma unroll
+        for (uint32_t m = 0; m < 4u; ++m) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xFFFFFFFFu, ss[m], o);
+            if (lane == 0) nm_part[m * (WARPS + 1) + warp] = ss[m];
+        }
+        __syncthreads();
+        if (threadIdx.x < 4u) {
+            float tot = 0.0f;
+            for (uint32_t w = 0; w <= (uint32_t)WARPS; ++w) tot += nm_part[threadIdx.x * (WARPS + 1) + w];
+            nm_inv[threadIdx.x] = rsqrtf(tot / (float)K + pre.eps);
+        }
+        __syncthreads();
+    }
+    // the eight bf16 activations 8u .. 8u+7 of row m
+    auto ld8 = [&](uint32_t m, uint32_t u) -> uint4 {
+        if constexpr (NORMED) {
+            const float4* xr = reinterpret_cast<const float4*>(x) + (size_t)m * (K >> 2) + 2u * u;
+            const float4 a = __ldg(xr), c = __ldg(xr + 1);
+            const uint4 gm = __ldg(reinterpret_cast<const uint4*>(pre.gamma) + u);
+            const float inv = nm_inv[m];
+            // the stand-alone norm kernel's arithmetic: x * inv * gamma, rounded to bf16
+            auto two = [&](float lo, float hi, uint32_t g2) {
+                return float_to_bf16_bits(lo * inv * bf16lo(g2)) | (float_to_bf16_bits(hi * inv * bf16hi(g2)) << 16);
+            };
+            return make_uint4(two(a.x, a.y, gm.x), two(a.z, a.w, gm.y), two(c.x, c.y, gm.z), two(c.z, c.w, gm.w));
+        } else {
+            return __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + u);
+        }
+    };
     bool staged = false;
     if constexpr (BITS == 4) {
         if constexpr (MP <= 4) {
             if (ROOMY || MP <= 2) {
-                stage_x_onepass<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+                stage_x_onepass<BITS, EXACT, MP, PAIR>(xs, xsum, M, K, steps_p, pitch, cpr, ld8);
                 staged = true;
             }
         } else if ((ROOMY || MP <= 2) && kslabs == 1u) {
-            stage_x_onepass_wide<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr);
+            stage_x_onepass_wide<BITS, EXACT, MP, PAIR>(xs, xsum, M, K, steps_p, pitch, cpr, ld8);
             staged = true;
         }
     }
-    if (!staged) stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, x_mul);
+    if (!staged) stage_x_padded<BITS, EXACT, MP, PAIR>(x, xs, xsum, M, K, steps_p, pitch, cpr, x_mul, ld8);
     for (uint32_t i = threadIdx.x; i < ZERO_BYTES / 16; i += THREADS)
         zeros[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
@@ -912,6 +969,9 @@ struct Shard {
     bool gated = false;
     // post-norm epilogue (4-bit weights, fp32 out, up to four rows, one GPU); residual null: off
     PostNorm post;
+    // norm prologue (4-bit weights, up to four rows, one GPU; fp32 out or the gated epilogue): x is
+    // fp32; gamma null: off
+    PreNorm pre;
 };
 
 // Launch plan: CTAs, active groups and stages per group; ngrp == 0 means the TMA path cannot
@@ -989,10 +1049,11 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
     if (rc) return rc;
     const uint8_t* ql = linear ? reinterpret_cast<const uint8_t*>(q) : nullptr;
     cudaError_t e = cudaSuccess;
-#define MIORI_TMA_LAUNCH(OB, SH, AM, GT, PN)                                                     \
+#define MIORI_TMA_LAUNCH(OB, SH, AM, GT, PN) MIORI_TMA_LAUNCH_N(OB, SH, AM, GT, PN, false)
+#define MIORI_TMA_LAUNCH_N(OB, SH, AM, GT, PN, NM)                                               \
     do {                                                                                         \
-        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM, GT, PN>  \
-                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM, GT, PN>;   \
+        auto kern = roomy ? gemv_tma_kernel<BITS, EXACT, NT, OB, SH, NT == 1, PAIR, AM, GT, PN, NM>  \
+                          : gemv_tma_kernel<BITS, EXACT, NT, OB, SH, false, PAIR, AM, GT, PN, NM>;   \
         e = cudaSuccess;                                                                         \
         if (smem_l > 48 * 1024)                                                                  \
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_l); \
@@ -1000,7 +1061,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
             e = launch(kern, dim3(grid), dim3(THREADS), smem_l, stream, pdl, tq, ts, tb, ql,     \
                        reinterpret_cast<const uint16_t*>(s), reinterpret_cast<const uint16_t*>(b), \
                        reinterpret_cast<const uint16_t*>(x), y, N, K, M, gshift, plan.ngrp, plan.nsg, plan.kpar, \
-                       sh.pa, placed ? sh.n_total : N, placed ? sh.row0 : 0u, sh.y_off, sh.best, sh.post); \
+                       sh.pa, placed ? sh.n_total : N, placed ? sh.row0 : 0u, sh.y_off, sh.best, sh.post, sh.pre); \
     } while (0)
     const bool sharded = sh.pa.world > 1;
     constexpr bool can_argmax = EXACT && NT == 1 && !PAIR;  // the one- and two-row kernels
@@ -1021,13 +1082,23 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
             else MIORI_TMA_LAUNCH(false, true, true, false, false);
         }
     }
+    const bool normed = sh.pre.gamma != nullptr;
+    if (normed && (BITS != 4 || !EXACT || sharded || argmax || postnorm || (!sh.gated && (flags & MIORI_OUT_BF16))))
+        return fail(MIORI_E_INVALID, "the norm prologue takes 4-bit weights, up to four rows, one GPU, fp32 out "
+                                     "or the gated epilogue");
+    if constexpr (BITS == 4 && EXACT) {
+        if (normed) {
+            if (sh.gated) MIORI_TMA_LAUNCH_N(true, false, false, true, false, true);
+            else MIORI_TMA_LAUNCH_N(false, false, false, false, false, true);
+        }
+    }
     if constexpr (BITS == 4) {
-        if (sh.gated) MIORI_TMA_LAUNCH(true, false, false, true, false);
+        if (sh.gated && !normed) MIORI_TMA_LAUNCH(true, false, false, true, false);
     }
     if constexpr (BITS == 4 && EXACT) {
         if (postnorm) MIORI_TMA_LAUNCH(false, false, false, false, true);
     }
-    if (!argmax && !sh.gated && !postnorm) {
+    if (!argmax && !sh.gated && !postnorm && !normed) {
         if (flags & MIORI_OUT_BF16) {
             if (sharded) MIORI_TMA_LAUNCH(true, true, false, false, false);
             else MIORI_TMA_LAUNCH(true, false, false, false, false);
@@ -1037,6 +1108,7 @@ int launch_one(Plan plan, const void* q, const void* s, const void* b, const voi
         }
     }
 #undef MIORI_TMA_LAUNCH
+#undef MIORI_TMA_LAUNCH_N
     if (e != cudaSuccess) return cuda_fail(e, "gemv_tma launch");
     return MIORI_OK;
 }

@@ -88,6 +88,21 @@ int gemv_rmsnorm_entry(const char* op, const void* q, const void* s, const void*
     if (!x || !y || !gamma) return fail(MIORI_E_INVALID, "%s: null activation, weight or output pointer", op);
     if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
     if (!aligned16(x) || !aligned16(gamma)) return fail(MIORI_E_INVALID, "%s: x and gamma must be 16-byte aligned", op);
+    // 4-bit weights, up to four rows, fp32 out, K within one slab: the TMA + mma.sync kernel with the norm
+    // in its staging pass (0.3-0.7 us faster than the pair of kernels; the tcgen05 kernel is slower than
+    // the pair there).  Longer rows and long streams go to the tcgen05 kernel (8192 -> 2048: 8.3 us
+    // against 10.3); the private flags force either.
+    if constexpr (BITS == 4) {
+        const bool long_stream = group == 64 && (N + 127u) / 128u >= 4u * (uint32_t)sm_count();
+        if (M <= 4 && !(flags & (MIORI_OUT_BF16 | MIORI_TUNE_GEMV_UMMA)) &&
+            ((!long_stream && K <= 2048u) || (flags & MIORI_TUNE_GEMV_MMASYNC))) {
+            gemvtma::Shard sh;
+            sh.pre.gamma = static_cast<const uint16_t*>(gamma);
+            sh.pre.eps = eps;
+            rc = gemvtma::try_launch<4>(q, s, b, x, y, N, K, M, group, flags, (cudaStream_t)stream, sh);
+            if (rc <= 0) return rc;  // launched (0) or failed (<0); 1 = not eligible: the tcgen05 kernel may be
+        }
+    }
     gemvumma::Placement pl;
     pl.gamma = gamma;
     pl.eps = eps;
@@ -116,6 +131,28 @@ MIORI_API int miori_gemv4_silu(const void* q, const void* s, const void* b, cons
     if (rc == 1)
         return fail(MIORI_E_INVALID, "%s: shape N=%u K=%u M=%u group=%u is outside the fused kernel's range "
                     "(run the plain GEMV and miori_silu_mul instead)", op, N, K, M, group);
+    return rc;
+}
+
+MIORI_API int miori_gemv4_rmsnorm_silu(const void* q, const void* s, const void* b, const void* x,
+                                       const void* gamma, float eps, void* y, uint32_t N, uint32_t K, uint32_t M,
+                                       uint32_t group, uint32_t flags, void* stream) {
+    const char* op = "miori_gemv4_rmsnorm_silu";
+    int rc = check_quant_args(op, q, s, b, N, K, group);
+    if (rc) return rc;
+    if (!x || !y || !gamma) return fail(MIORI_E_INVALID, "%s: null activation, weight or output pointer", op);
+    if (M == 0 || M > 4) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..4", op, M);
+    if (!aligned16(x) || !aligned16(gamma)) return fail(MIORI_E_INVALID, "%s: x and gamma must be 16-byte aligned", op);
+    if (N % 16 != 0)
+        return fail(MIORI_E_INVALID, "%s: N=%u (gate rows then up rows) must be a multiple of 16", op, N);
+    gemvtma::Shard sh;
+    sh.gated = true;
+    sh.pre.gamma = static_cast<const uint16_t*>(gamma);
+    sh.pre.eps = eps;
+    rc = gemvtma::try_launch<4>(q, s, b, x, y, N, K, M, group, flags | MIORI_OUT_BF16, (cudaStream_t)stream, sh);
+    if (rc == 1)
+        return fail(MIORI_E_INVALID, "%s: shape N=%u K=%u M=%u group=%u is outside the fused kernel's range "
+                    "(run miori_rmsnorm and miori_gemv4_silu instead)", op, N, K, M, group);
     return rc;
 }
 

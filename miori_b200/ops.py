@@ -248,3 +248,19 @@ def gemv4_post_norm_add(q, s, b, x, residual, gamma, eps, counter, group=32, fla
                                         gamma.data_ptr(), float(eps), counter.data_ptr(), o.data_ptr(), N, K, M,
                                         group, flags, _stream()))
     return o
+
+
+def gemv4_rmsnorm_silu(q, s, b, x, gamma, eps, group=32, flags=0, out=None):
+    """bf16(silu(gate) * up) [M][N/2] of the fused gate + up weights applied to bf16(rmsnorm(x) * gamma),
+    x fp32 [M][K], M <= 4: one launch for the norm, both projections and the activation."""
+    _need_cuda(q, s, b, x, gamma)
+    if x.dtype != torch.float32:
+        raise TypeError("the fused norm takes fp32 activations")
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    M, K = x.shape
+    N = q.shape[0]
+    y = out if out is not None else torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    check(lib.miori_gemv4_rmsnorm_silu(q.data_ptr(), s.data_ptr(), b.data_ptr(), x.data_ptr(), gamma.data_ptr(),
+                                       float(eps), y.data_ptr(), N, K, M, group, flags, _stream()))
+    return y

@@ -119,6 +119,10 @@ def test_neighbor_and_narrow_batch_entries_reject_bad_arguments():
     assert lib.miori_gemv4_post_norm_add(ok, ok, ok, ok, ok, ok, 1e-5, ok, ok, 32, 64, 1, 32, 0, None) == -1
     assert b"residual" in lib.miori_last_error()
     assert lib.miori_gemv4_post_norm_add(ok, ok, ok, ok, ok + 64, ok, 1e-5, ok, ok, 32, 64, 1, 32, 1, None) == -1
+    assert lib.miori_gemv4_rmsnorm_silu(ok, ok, ok, ok, ok, 1e-5, ok, 32, 64, 5, 32, 0, None) == -1
+    assert b"1..4" in lib.miori_last_error()
+    assert lib.miori_gemv4_rmsnorm_silu(ok, ok, ok, ok, None, 1e-5, ok, 32, 64, 1, 32, 0, None) == -1
+    assert lib.miori_gemv4_rmsnorm_silu(ok, ok, ok, ok, ok, 1e-5, ok, 24, 64, 1, 32, 0, None) == -1
     assert lib.miori_rmsnorm(None, ok, ok, 1, 64, 1e-5, 0, None) == -1
     assert lib.miori_rmsnorm(ok, ok, ok, 0, 64, 1e-5, 0, None) == -1
     assert lib.miori_argmax(ok, 0, 0, ok, ok, None) == -1

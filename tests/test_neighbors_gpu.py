@@ -103,16 +103,19 @@ def test_argmax_sizes_and_alignment(n, dtype):
 
 
 @pytest.mark.parametrize("bits,N,K,M,group", [(4, 2048, 2048, 1, 64), (4, 3072, 2048, 4, 32), (4, 640, 2048, 8, 64),
-                                              (8, 1024, 2048, 2, 64), (4, 2048, 8192, 1, 64), (4, 1536, 2048, 32, 64)])
-def test_gemv_with_fused_rmsnorm(port, bits, N, K, M, group):
-    """y = W * bf16(rmsnorm(x)): the fused kernel against the oracle's norm followed by its GEMV,
-    and against this library's own unfused pair."""
+                                              (8, 1024, 2048, 2, 64), (4, 2048, 8192, 1, 64), (4, 1536, 2048, 32, 64),
+                                              (4, 16384, 2048, 2, 64), (4, 1000, 4096, 3, 64), (4, 48, 512, 3, 32)])
+@pytest.mark.parametrize("force", [0, 0x100000, 0x1000], ids=["default", "tcgen05", "mma.sync"])
+def test_gemv_with_fused_rmsnorm(port, bits, N, K, M, group, force):
+    """y = W * bf16(rmsnorm(x)): the fused kernels (by default the TMA + mma.sync one for 4-bit weights,
+    up to four rows and K <= 2048, the tcgen05 one otherwise; either when forced, where it applies)
+    against the oracle's norm followed by its GEMV, and against this library's own unfused pair."""
     q, s, b = synth.make_weight(N, K, bits, group, seed=N + K + M)
     g = torch.Generator().manual_seed(M)
     x = torch.randn((M, K), generator=g) * 2.5
     w = (torch.randn(K, generator=g) * 0.2 + 1.0).to(torch.bfloat16)
     fused = (miori_b200.gemv4_rmsnorm if bits == 4 else miori_b200.gemv8_rmsnorm)(
-        q.to(DEV), s.to(DEV), b.to(DEV), x.to(DEV), w.to(DEV), 1e-5, group=group).cpu().numpy()
+        q.to(DEV), s.to(DEV), b.to(DEV), x.to(DEV), w.to(DEV), 1e-5, group=group, flags=force).cpu().numpy()
     xn = port.rmsnorm(x.numpy(), u16(w), 1e-5)
     want = port.gemv(bits, u32(q), u16(s), u16(b), xn, group)
     # a bf16 rounding of a normalised activation may tip differently than in the oracle (fp32 order
@@ -216,3 +219,28 @@ def test_gemv_with_post_norm_add_epilogue_refuses_what_it_cannot_take():
     with pytest.raises(miori_b200.MioriError, match="must not be the residual"):
         miori_b200.gemv4_post_norm_add(q.to(DEV), s.to(DEV), b.to(DEV), x[:1].contiguous(), res[:1], w, 1e-5,
                                        counter, group=64, out=res[:1])
+
+
+@pytest.mark.parametrize("N,K,M,group,flags", [(16384, 2048, 1, 64, 0), (4096, 2048, 2, 32, 0), (12288, 2048, 3, 64, 0),
+                                               (2048, 4096, 4, 64, 0), (1024, 2048, 1, 64, TILED), (32, 512, 4, 64, 0)])
+def test_gate_up_projection_with_both_neighbours(port, N, K, M, group, flags):
+    """rmsnorm, w1, w3 and silu_mul in one launch, against this library's own chain (norm kernel, then
+    the gated GEMV) and against the oracle's."""
+    q, s, b = synth.make_weight(N, K, 4, group, seed=N + K + M)
+    g = torch.Generator().manual_seed(M + 11)
+    x = torch.randn((M, K), generator=g) * 1.5
+    w = (torch.randn(K, generator=g) * 0.2 + 1.0).to(torch.bfloat16)
+    dq, ds, db, dx, dw = q.to(DEV), s.to(DEV), b.to(DEV), x.to(DEV), w.to(DEV)
+    fused = miori_b200.gemv4_rmsnorm_silu(dq, ds, db, dx, dw, 1e-5, group=group, flags=flags)
+    assert fused.shape == (M, N // 2) and fused.dtype == torch.bfloat16
+    chain = miori_b200.gemv4_silu(dq, ds, db, miori_b200.rmsnorm(dx, dw, 1e-5), group=group, flags=flags)
+    got = fused.float().cpu().numpy()
+    # a bf16 rounding of a normalised activation may tip differently (fp32 order of the sum of squares)
+    assert_close(got, chain.float().cpu().numpy(), rel_max=1e-2, what="one launch vs norm kernel + gated GEMV")
+    xn = port.rmsnorm(x.numpy(), u16(w), 1e-5)
+    want_y = port.gemv(4, u32(q), u16(s), u16(b), xn, group)
+    h = N // 2
+    want = port.silu_mul(np.ascontiguousarray(want_y[:, :h]), np.ascontiguousarray(want_y[:, h:]))
+    ref = (want.astype(np.uint32) << 16).view(np.float32).reshape(got.shape)
+    assert_close(got, ref, rel_max=1e-2, what=f"norm + gated gemv4 M={M}")
+    assert miori_b200.lib.miori_device_error_poll() == 0
