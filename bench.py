@@ -246,6 +246,10 @@ def run_one(a):
         ms = time_ms(lambda: [fn(q, s, b, xf, gamma, 1e-5, group=G, flags=a.flags, out=y) for q, s, b in pool])
         print(f"gemv{bits}_rmsnorm N={a.n} K={a.k} M={a.m} g={G}: {ms * 1e3:.2f} us/launch "
               f"{wbytes / ms / 1e6:.0f} GB/s")
+    elif a.one == "gemv_silu":
+        act = torch.empty((a.m, a.n // 2), dtype=torch.bfloat16, device=dev)
+        ms = time_ms(lambda: [miori_b200.gemv4_silu(q, s, b, x, group=G, flags=a.flags, out=act) for q, s, b in pool])
+        print(f"gemv4_silu N={a.n} K={a.k} M={a.m} g={G}: {ms * 1e3:.2f} us/launch {wbytes / ms / 1e6:.0f} GB/s")
     elif a.one == "dequant":
         out = torch.empty((a.n, a.k), dtype=torch.bfloat16, device=dev)
         ms = time_ms(lambda: [miori_b200.dequant4_rowmajor(q, s, b, group=G, out=out) for q, s, b in pool])
@@ -303,7 +307,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="stack depth (24 is the benchmark)")
     ap.add_argument("--verbose", action="store_true", help="progress on stderr")
     one = ap.add_argument_group("one operator on one GPU (--one): a small case to time or to profile")
-    one.add_argument("--one", choices=["gemv", "gemv_rmsnorm", "gemm", "gemv_cache", "dequant"])
+    one.add_argument("--one", choices=["gemv", "gemv_rmsnorm", "gemv_silu", "gemm", "gemv_cache", "dequant"])
     one.add_argument("--bits", type=int, default=4, choices=[4, 8])
     one.add_argument("--n", type=int, default=8192)
     one.add_argument("--k", type=int, default=2048)

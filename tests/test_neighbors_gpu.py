@@ -1,6 +1,7 @@
 """The steps either side of a projection (RMSNorm, SiLU x up, post-norm + residual), the 8-bit
-embedding gather, the arg-max, and the GEMV with the RMSNorm fused into its activation staging,
-against the CPU restatements of the reference's shaders (oracle/miori_oracle.c)."""
+embedding gather, the arg-max, and the GEMVs that take those steps in (the RMSNorm in the activation
+staging, SiLU x up and the post-norm as epilogues), against the CPU restatements of the reference's
+shaders (oracle/miori_oracle.c)."""
 import numpy as np
 import pytest
 import torch
