@@ -243,6 +243,78 @@ __device__ __forceinline__ void stage_x_onepass_wide(uint4* xs, float* xsum, uin
     }
 }
 
+// Staging with the RMSNorm in it (shaders/ops.metal:86-115), rows of K <= 2048: x is fp32.  Thread
+// i < K/4 loads piece i (four activations) of every row together with its four norm weights -- one
+// trip to L2 for everything, which matters because every CTA of the grid asks for the same lines at
+// the same moment -- the warps add up the rows' squares (shuffles, 16 warp sums per row through
+// shared memory, every thread adds them in order), and each thread normalises its piece with the
+// stand-alone kernel's arithmetic, x * inv * gamma rounded to bf16.  Lane pairs then form the
+// eight-activation units of the plain staging (permuted store, and for EXACT the fp32 sum over
+// every chunk resp. chunk pair, added up in the plain staging's order).
+template <bool EXACT, int MP, bool PAIR>
+__device__ __forceinline__ void stage_x_normed(const float* __restrict__ x, const uint16_t* __restrict__ gamma,
+                                               float eps, uint4* xs, float* xsum, uint32_t M, uint32_t K,
+                                               uint32_t pitch, uint32_t cpr, float* part) {
+    static_assert(MP <= 4, "rows of the norm prologue");
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t qpr = K >> 2;  // pieces per row, at most 512
+    const bool mine = tid < qpr;
+    float4 v[MP];
+    uint2 gq = make_uint2(0u, 0u);
+    if (mine) gq = __ldg(reinterpret_cast<const uint2*>(gamma) + tid);
+#pragma unroll
+    for (int m = 0; m < MP; ++m) {
+        v[m] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (mine && (uint32_t)m < M) v[m] = __ldg(reinterpret_cast<const float4*>(x) + (size_t)m * qpr + tid);
+    }
+    // units past K and rows past M read as zeros
+    for (uint32_t i = tid; i < (uint32_t)MP * pitch; i += THREADS) xs[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (EXACT)
+        for (uint32_t i = tid; i < (uint32_t)MP * cpr; i += THREADS) xsum[i] = 0.0f;
+    if (warp < 16u) {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            float ss = __fmaf_rn(v[m].w, v[m].w, __fmaf_rn(v[m].z, v[m].z, __fmaf_rn(v[m].y, v[m].y, v[m].x * v[m].x)));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            if (lane == 0) part[m * 16 + warp] = ss;
+        }
+    }
+    __syncthreads();
+    if (warp >= 16u) return;
+#pragma unroll
+    for (int m = 0; m < MP; ++m) {
+        if ((uint32_t)m >= M) break;  // CTA-uniform
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 16; ++w) tot += part[m * 16 + w];
+        const float inv = rsqrtf(tot / (float)K + eps);
+        const uint32_t lo = float_to_bf16_bits(v[m].x * inv * bf16lo(gq.x)) |
+                            (float_to_bf16_bits(v[m].y * inv * bf16hi(gq.x)) << 16);
+        const uint32_t hi = float_to_bf16_bits(v[m].z * inv * bf16lo(gq.y)) |
+                            (float_to_bf16_bits(v[m].w * inv * bf16hi(gq.y)) << 16);
+        // the even lane of a pair collects the unit: activations 8u .. 8u+7, u = tid / 2
+        const uint32_t olo = __shfl_down_sync(0xFFFFFFFFu, lo, 1), ohi = __shfl_down_sync(0xFFFFFFFFu, hi, 1);
+        const uint32_t u = tid >> 1;
+        if (mine && (tid & 1u) == 0u) {
+            uint4 o;
+            o.x = __byte_perm(lo, olo, 0x5410);  // (x0,x4)
+            o.y = __byte_perm(lo, olo, 0x7632);  // (x1,x5)
+            o.z = __byte_perm(hi, ohi, 0x5410);  // (x2,x6)
+            o.w = __byte_perm(hi, ohi, 0x7632);  // (x3,x7)
+            xs[(size_t)m * pitch + x_unit(u >> 4, (u >> 2) & 3u, u & 3u)] = o;
+        }
+        if (EXACT) {
+            float sum = (bf16lo(lo) + bf16hi(lo)) + (bf16lo(hi) + bf16hi(hi));
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);  // the unit
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);  // the chunk of 32
+            if (PAIR) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
+            if (mine && (tid & 7u) == 0u) xsum[m * cpr + (tid >> 3)] = sum;
+        }
+    }
+}
+
 // ROOMY: compiled for one CTA per SM (up to 120 registers instead of 56).  Problems of at most
 // two tiles per SM run 4-18 % faster that way (no spills, freer scheduling); long streams prefer
 // two CTAs per SM.
@@ -540,9 +612,15 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __shared__ float nm_part[NORMED ? 4 * (WARPS + 1) : 1];
     __shared__ float nm_inv[4];
     if constexpr (NORMED) {
-        // sums of squares of the (at most four) rows: all loads in flight together, warps reduce by
-        // shuffles, one thread per row adds the warp sums in order
-        static_assert(MP <= 4, "rows of the norm prologue");
+        if (K <= 2048u)
+            stage_x_normed<EXACT, MP, PAIR>(reinterpret_cast<const float*>(x), pre.gamma, pre.eps, xs, xsum, M, K,
+                                            pitch, cpr, nm_part);
+    }
+    if (NORMED && K > 2048u) {
+        // longer rows: sums of squares of the (at most four) rows first -- all loads in flight together,
+        // warps reduce by shuffles, one thread per row adds the warp sums in order -- then the plain
+        // staging passes with a loader that normalises
+        static_assert(!NORMED || MP <= 4, "rows of the norm prologue");
         const float4* x4 = reinterpret_cast<const float4*>(x);
         const uint32_t qpr = K >> 2;  // float4 pieces per row (K is a multiple of 32)
         float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -586,8 +664,10 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     };
     bool staged = false;
+    if constexpr (NORMED) staged = K <= 2048u;  // staged above, norm included
     if constexpr (BITS == 4) {
-        if constexpr (MP <= 4) {
+        if (staged) {
+        } else if constexpr (MP <= 4) {
             if (ROOMY || MP <= 2) {
                 stage_x_onepass<BITS, EXACT, MP, PAIR>(xs, xsum, M, K, steps_p, pitch, cpr, ld8);
                 staged = true;

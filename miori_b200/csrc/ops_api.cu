@@ -89,7 +89,7 @@ int gemv_rmsnorm_entry(const char* op, const void* q, const void* s, const void*
     if (M == 0 || M > 32) return fail(MIORI_E_INVALID, "%s: M=%u outside 1..32", op, M);
     if (!aligned16(x) || !aligned16(gamma)) return fail(MIORI_E_INVALID, "%s: x and gamma must be 16-byte aligned", op);
     // 4-bit weights, up to four rows, fp32 out, K within one slab: the TMA + mma.sync kernel with the norm
-    // in its staging pass (0.3-0.7 us faster than the pair of kernels; the tcgen05 kernel is slower than
+    // in its staging pass (1.2-1.6 us faster than the pair of kernels; the tcgen05 kernel is slower than
     // the pair there).  Longer rows and long streams go to the tcgen05 kernel (8192 -> 2048: 8.3 us
     // against 10.3); the private flags force either.
     if constexpr (BITS == 4) {
