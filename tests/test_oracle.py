@@ -128,3 +128,32 @@ def test_quantizer_matches_torch_generator(port):
         w = port.bf16_to_float(port.dequant_rowmajor(bits, qb, sb, bb, group))
         step = port.bf16_to_float(sb).repeat(group, axis=1)
         assert (np.abs(w - W.numpy()) <= 0.75 * step + 1e-3).all()
+
+
+def test_known_answers_of_the_projection_neighbours(port):
+    """rmsnorm, silu_mul, post_norm_add and embed8 (shaders/ops.metal:86-115, 129-139, 605-631, 170-197)
+    on inputs whose results can be written down by hand."""
+    bf = lambda *v: port.float_to_bf16(np.array(v, np.float32))
+    # rmsnorm: mean(x^2) = 4, eps = 0 -> inv = 1/2; y = x * 0.5 * w
+    y = port.rmsnorm(np.array([[2.0, -2.0, 2.0, -2.0]], np.float32), bf(1.0, 1.0, 0.5, 3.0), 0.0)
+    assert y.tolist() == [[0x3F80, 0xBF80, 0x3F00, 0xC040]]           # 1, -1, 0.5, -3
+    # eps alone under the root: x = 0 stays 0; x = 1 with eps = 3 -> 1/sqrt(1 + 3) = 0.5
+    assert port.rmsnorm(np.zeros((1, 4), np.float32), bf(1, 1, 1, 1), 1e-5).tolist() == [[0, 0, 0, 0]]
+    assert port.rmsnorm(np.ones((1, 2), np.float32), bf(1.0, 2.0), 3.0).tolist() == [[0x3F00, 0x3F80]]
+    # silu_mul: silu(0) = 0; silu(ln 3) = 0.75 ln 3 = 0.82396 -> bf16 0x3F53 (0.82422; 0x3F52 is 0.82031);
+    # a large gate passes through (silu(100) = 100 in fp32), a large negative one gives -0 * up = -0 or 0
+    g = np.array([0.0, np.log(3.0), 100.0, 100.0], np.float32)
+    u = np.array([5.0, 1.0, 1.0, -0.5], np.float32)
+    assert port.silu_mul(g, u).tolist() == [0x0000, 0x3F53, 0x42C8, 0xC248]   # 0, 0.824, 100, -50
+    assert port.silu_mul(np.array([-100.0], np.float32), np.array([1.0], np.float32))[0] & 0x7FFF == 0
+    # post_norm_add: src = (2, -2): mean square 4, inv = 0.5 -> x + src * 0.5 * w
+    out = port.post_norm_add(np.array([[1.0, 2.0]], np.float32), np.array([[2.0, -2.0]], np.float32), bf(1.0, 0.5), 0.0)
+    assert out.tolist() == [[2.0, 1.5]]
+    # embed8: row 1 of a two-row table, codes 0, 1, 2, 3 and 255 with scale 0.5, bias -1
+    q = np.zeros((2, 8), np.uint32)
+    q[1, 0], q[1, 1] = 0x03020100, 0x000000FF
+    s, b = np.tile(bf(0.5), (2, 1)), np.tile(bf(-1.0), (2, 1))
+    e = port.embed8(q, s, b, np.array([1, 0], np.uint32), 32)
+    assert e.shape == (2, 32)
+    assert e[0, :5].tolist() == [0xBF80, 0xBF00, 0x0000, 0x3F00, 0x42FD]     # -1, -0.5, 0, 0.5, 126.5
+    assert (e[1] == 0xBF80).all()                                            # row 0: all codes 0 -> -1
