@@ -982,7 +982,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap_q,
             float* out = reinterpret_cast<float*>(y);
             for (uint32_t m = 0; m < M; ++m) {
                 const size_t at = (size_t)m * N;
-                neighbors::post_norm_add_row<9, true>(pn.residual + at, out + at, pn.gamma, out + at, N, pn.eps, pn_part);
+                if (N <= 8u * (uint32_t)neighbors::NORM_THREADS)
+                    neighbors::post_norm_add_row_regs<9, true, 8>(pn.residual + at, out + at, pn.gamma, out + at, N,
+                                                                  pn.eps, pn_part);
+                else
+                    neighbors::post_norm_add_row<9, true>(pn.residual + at, out + at, pn.gamma, out + at, N, pn.eps,
+                                                          pn_part);
                 neighbors::norm_sync<9>();  // pn_part is reused by the next row
             }
             if (threadIdx.x == 0) *pn.arrivals = 0u;  // ready for the next launch

@@ -52,5 +52,42 @@ __device__ __forceinline__ void post_norm_add_row(const float* x, const float* s
         out[i] = x[i] + norm_load<FRESH>(src, i) * inv * bf16_bits_to_float(w[i]);
 }
 
+// The same for rows of at most NORM_THREADS * PER elements, with every load of the row issued before
+// the first use -- one trip to memory instead of two dependent ones.  Same sums in the same order,
+// same expression: the same bits.
+template <int BAR, bool FRESH, int PER>
+__device__ __forceinline__ void post_norm_add_row_regs(const float* x, const float* src, const uint16_t* w,
+                                                       float* out, uint32_t n, float eps, float* part) {
+    float v[PER], r[PER];
+    uint16_t g[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const uint32_t i = threadIdx.x + (uint32_t)j * NORM_THREADS;
+        v[j] = 0.0f, r[j] = 0.0f, g[j] = 0;
+        if (i < n) {
+            v[j] = norm_load<FRESH>(src, i);
+            r[j] = x[i];
+            g[j] = w[i];
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j)
+        if (threadIdx.x + (uint32_t)j * NORM_THREADS < n) ss = __fmaf_rn(v[j], v[j], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = ss;
+    norm_sync<BAR>();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NORM_THREADS / 32; ++i) tot += part[i];
+    const float inv = rsqrtf(tot / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const uint32_t i = threadIdx.x + (uint32_t)j * NORM_THREADS;
+        if (i < n) out[i] = r[j] + v[j] * inv * bf16_bits_to_float(g[j]);
+    }
+}
+
 }  // namespace neighbors
 }  // namespace miori_b200
