@@ -16,6 +16,11 @@
 // CTA-wide barrier in the main loop.  A 17th warp is the TMA producer: one of its threads
 // refills a stage as soon as its group hands it back.  Out-of-range rows and columns are
 // zero-filled by TMA, which makes every code, scale and bias there contribute exactly 0.
+//
+// Optional neighbours of the projection, each a template parameter so that the plain instantiation
+// is compiled as if they did not exist: NORMED (RMSNorm of fp32 activations inside the staging pass),
+// GATED (SiLU x up behind the fused gate + up rows), POSTNORM (post-norm and residual add by the CTA
+// that finishes last), ARGMAX (greedy pick of a sharded head).
 #pragma once
 #include "common.cuh"
 #include "gemv_mma.cuh"
