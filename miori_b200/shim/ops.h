@@ -77,6 +77,11 @@ void silu_mul(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* gate, MTL::B
 void embed8(Metal& m, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q,
             const Tensor& s, const Tensor& b, MTL::Buffer* tokens, MTL::Buffer* out, uint32_t T,
             uint32_t K);
+// reference src/ops.h:109-111 -- out (f32) = x + src * rsqrt(mean(src^2) + eps) * gamma, row by row;
+// out may be x (the engine updates its residual stream in place, src/engine.cpp:384-386)
+void postnorm_add(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* x, MTL::Buffer* src, const Weights& w,
+                  const Tensor& gamma, MTL::Buffer* out, uint32_t rows, uint32_t n, float eps);
+
 // reference src/ops.h:207-209 -- the small-M tile shape; same kernel, same result per row
 void gemm_mpp32(Metal& m, MTL::ComputeCommandEncoder* e, MTL::Buffer* A, MTL::Buffer* B,
                 MTL::Buffer* C, uint32_t M, uint32_t N, uint32_t K, uint32_t boff = 0);

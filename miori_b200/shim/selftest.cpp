@@ -2,6 +2,7 @@
 // (reference src/main.cpp:44-87 test-gemv4/8, :1403-1443 test-mpp-tile), for the Python
 // tests: host arrays in, host arrays out, everything in between through miori::Metal,
 // miori::Weights and the miori:: operators.
+#include "fused_ops.h"
 #include "ops.h"
 
 #include <cstring>
@@ -174,6 +175,83 @@ extern "C" __attribute__((visibility("default"))) int miori_shim_test_neighbors(
         std::memcpy(norm_out, bn->contents(), (size_t)rows * K * 2);
         std::memcpy(act_out, ba->contents(), (size_t)n_act * 2);
         for (MTL::Buffer* b : {btok, bemb, bx, bn, bg, bu, ba}) b->release();
+        return 0;
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return -1;
+    }
+}
+
+// The feed-forward block of a decode step (reference src/engine.cpp:388-399: rmsnorm, w1, w3,
+// silu_mul, w2, post-norm added onto the residual in place) through the operator API, three ways:
+// the reference's six operators; the gate + up weights as one tensor with the activation as the
+// GEMV's epilogue; the norm in front of that GEMV as well.  q13/s13/b13 hold w1's F rows followed by
+// w3's; every variant starts from its own copy of the residual x and leaves the new residual there.
+extern "C" __attribute__((visibility("default"))) int miori_shim_test_ffn(
+    const uint32_t* q13, const uint16_t* s13, const uint16_t* b13, const uint32_t* q2, const uint16_t* s2,
+    const uint16_t* b2, const uint16_t* gamma_in, const uint16_t* gamma_post, const float* x, uint32_t F,
+    uint32_t H, float eps, float* out_six_ops, float* out_gated, float* out_normed_gated) {
+    using namespace miori;
+    try {
+        Metal m;
+        std::string err;
+        if (!m.init("", err)) throw std::runtime_error(err);
+        Weights w;
+        const size_t q13b = (size_t)2 * F * H / 2, s13b = (size_t)2 * F * (H / kGroup) * 2;
+        const size_t q2b = (size_t)H * F / 2, s2b = (size_t)H * (F / kGroup) * 2;
+        if (!w.reserve(m, q13b + 2 * s13b + q2b + 2 * s2b + (size_t)4 * H + 4096, err)) throw std::runtime_error(err);
+        const Tensor& tq13 = w.add("w13.weight", "U32", {(int64_t)2 * F, (int64_t)(H / 8)}, q13, q13b);
+        const Tensor& ts13 = w.add("w13.scales", "BF16", {(int64_t)2 * F, (int64_t)(H / kGroup)}, s13, s13b);
+        const Tensor& tb13 = w.add("w13.biases", "BF16", {(int64_t)2 * F, (int64_t)(H / kGroup)}, b13, s13b);
+        const Tensor& tq2 = w.add("w2.weight", "U32", {(int64_t)H, (int64_t)(F / 8)}, q2, q2b);
+        const Tensor& ts2 = w.add("w2.scales", "BF16", {(int64_t)H, (int64_t)(F / kGroup)}, s2, s2b);
+        const Tensor& tb2 = w.add("w2.biases", "BF16", {(int64_t)H, (int64_t)(F / kGroup)}, b2, s2b);
+        const Tensor& tgi = w.add("ffn_norm.weight", "BF16", {(int64_t)H}, gamma_in, (size_t)H * 2);
+        const Tensor& tgp = w.add("post_ffn_norm.weight", "BF16", {(int64_t)H}, gamma_post, (size_t)H * 2);
+        // w1 and w3 as the halves of the fused tensors (rows are contiguous)
+        auto half = [&](const Tensor& t, int which) {
+            Tensor h = t;
+            const uint64_t mid = t.begin + (t.end - t.begin) / 2;
+            h.shape[0] = t.shape[0] / 2;
+            if (which == 0) h.end = mid; else h.begin = mid;
+            return h;
+        };
+        const Tensor q1 = half(tq13, 0), s1 = half(ts13, 0), b1 = half(tb13, 0);
+        const Tensor q3 = half(tq13, 1), s3 = half(ts13, 1), b3 = half(tb13, 1);
+        MTL::Buffer* xs[3];
+        for (auto& bx : xs) {
+            bx = m.new_buffer((size_t)H * 4);
+            std::memcpy(bx->contents(), x, (size_t)H * 4);
+        }
+        MTL::Buffer* h = m.new_buffer((size_t)H * 2);
+        MTL::Buffer* fg = m.new_buffer((size_t)F * 4);
+        MTL::Buffer* fu = m.new_buffer((size_t)F * 4);
+        MTL::Buffer* fact = m.new_buffer((size_t)F * 2);
+        MTL::Buffer* down = m.new_buffer((size_t)H * 4);
+        auto* cb = m.begin();
+        auto* e = cb->computeCommandEncoder();
+        // the reference's operators
+        rmsnorm(m, e, xs[0], w, tgi, h, 1, H, eps);
+        gemv4(m, e, w, q1, s1, b1, h, fg, F, H);
+        gemv4(m, e, w, q3, s3, b3, h, fu, F, H);
+        silu_mul(m, e, fg, fu, fact, F);
+        gemv4(m, e, w, tq2, ts2, tb2, fact, down, H, F);
+        postnorm_add(m, e, xs[0], down, w, tgp, xs[0], 1, H, eps);
+        // gate + up in one launch with the activation
+        rmsnorm(m, e, xs[1], w, tgi, h, 1, H, eps);
+        gemv4_silu(m, e, w, tq13, ts13, tb13, h, fact, 2 * F, H);
+        gemv4(m, e, w, tq2, ts2, tb2, fact, down, H, F);
+        postnorm_add(m, e, xs[1], down, w, tgp, xs[1], 1, H, eps);
+        // and with the norm in front
+        gemv4_rmsnorm_silu(m, e, w, tq13, ts13, tb13, xs[2], tgi, eps, fact, 2 * F, H);
+        gemv4(m, e, w, tq2, ts2, tb2, fact, down, H, F);
+        postnorm_add(m, e, xs[2], down, w, tgp, xs[2], 1, H, eps);
+        e->endEncoding();
+        m.submit(cb, true);
+        std::memcpy(out_six_ops, xs[0]->contents(), (size_t)H * 4);
+        std::memcpy(out_gated, xs[1]->contents(), (size_t)H * 4);
+        std::memcpy(out_normed_gated, xs[2]->contents(), (size_t)H * 4);
+        for (MTL::Buffer* b : {xs[0], xs[1], xs[2], h, fg, fu, fact, down}) b->release();
         return 0;
     } catch (const std::exception& ex) {
         g_err = ex.what();

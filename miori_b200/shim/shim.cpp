@@ -1,5 +1,6 @@
 // Bodies of the CUDA-backed runtime, weights registry and hot-path operators declared in
 // metal.h / weights.h / ops.h, all on top of the C ABI (include/miori_b200.h).
+#include "fused_ops.h"
 #include "ops.h"
 
 #include "miori_b200.h"
@@ -230,6 +231,38 @@ void rmsnorm(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* x, const Weight
 void silu_mul(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* gate, MTL::Buffer* up, MTL::Buffer* out,
               uint32_t n) {
     check(miori_silu_mul(at(gate, 0), at(up, 0), at_mut(out, 0), n, 0, e->stream()), "silu_mul");
+}
+
+void postnorm_add(Metal&, MTL::ComputeCommandEncoder* e, MTL::Buffer* x, MTL::Buffer* src, const Weights& w,
+                  const Tensor& gamma, MTL::Buffer* out, uint32_t rows, uint32_t n, float eps) {
+    check(miori_post_norm_add(at(x, 0), at(src, 0), at(w.buffer(), gamma.begin), at_mut(out, 0), rows, n, eps, 0,
+                              e->stream()),
+          "postnorm_add");
+}
+
+void gemv4_silu(Metal&, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q, const Tensor& s,
+                const Tensor& b, MTL::Buffer* x, MTL::Buffer* y, uint32_t N, uint32_t K, uint32_t B) {
+    check(miori_gemv4_silu(at(w.buffer(), q.begin), at(w.buffer(), s.begin), at(w.buffer(), b.begin), x->gpu(),
+                           y->gpu(), N, K, B, kGroup, 0, e->stream()),
+          "gemv4_silu");
+}
+
+void gemv4_rmsnorm(Metal&, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q, const Tensor& s,
+                   const Tensor& b, MTL::Buffer* x, const Tensor& gamma, float eps, MTL::Buffer* y, uint32_t N,
+                   uint32_t K, uint32_t B) {
+    check(miori_gemv4_rmsnorm(at(w.buffer(), q.begin), at(w.buffer(), s.begin), at(w.buffer(), b.begin), x->gpu(),
+                              at(w.buffer(), gamma.begin), eps, y->gpu(), N, K, B, kGroup, MIORI_OUT_F32,
+                              e->stream()),
+          "gemv4_rmsnorm");
+}
+
+void gemv4_rmsnorm_silu(Metal&, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q, const Tensor& s,
+                        const Tensor& b, MTL::Buffer* x, const Tensor& gamma, float eps, MTL::Buffer* y,
+                        uint32_t N, uint32_t K, uint32_t B) {
+    check(miori_gemv4_rmsnorm_silu(at(w.buffer(), q.begin), at(w.buffer(), s.begin), at(w.buffer(), b.begin),
+                                   x->gpu(), at(w.buffer(), gamma.begin), eps, y->gpu(), N, K, B, kGroup, 0,
+                                   e->stream()),
+          "gemv4_rmsnorm_silu");
 }
 
 void embed8(Metal&, MTL::ComputeCommandEncoder* e, const Weights& w, const Tensor& q, const Tensor& s,

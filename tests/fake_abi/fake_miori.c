@@ -74,3 +74,7 @@ LAUNCH(miori_gemm_bf16_strided)
 LAUNCH(miori_rmsnorm)
 LAUNCH(miori_silu_mul)
 LAUNCH(miori_embed8)
+LAUNCH(miori_post_norm_add)
+LAUNCH(miori_gemv4_silu)
+LAUNCH(miori_gemv4_rmsnorm)
+LAUNCH(miori_gemv4_rmsnorm_silu)

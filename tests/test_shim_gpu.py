@@ -117,3 +117,34 @@ def test_neighbors_through_operator_api(shim, port):
         return np.abs(a.astype(np.int32) - w.astype(np.int32)).max()
     assert ulps(norm, port.rmsnorm(x, gamma, 1e-5)) <= 1
     assert ulps(act, port.silu_mul(gate, up)) <= 1
+
+
+def test_ffn_block_through_operator_api(shim, port):
+    """The feed-forward block of a decode step (src/engine.cpp:388-399) encoded with the reference's
+    six operators, with the gate + up GEMV that carries the activation, and with the norm in front of
+    it too: the first two agree bit for bit, the third to the rounding of the normalised activations,
+    and all follow the oracle's chain."""
+    F, H = 1536, 2048
+    q13, s13, b13 = synth.make_weight(2 * F, H, 4, 32, seed=51)
+    q2, s2, b2 = synth.make_weight(H, F, 4, 32, seed=52)
+    g = np.random.default_rng(9)
+    x = g.standard_normal(H).astype(np.float32) * 2.0
+    gi = u16(synth.make_activation(1, H, seed=6)).reshape(-1)
+    gp = u16(synth.make_activation(1, H, seed=7)).reshape(-1)
+    arrs = [u32(q13), u16(s13), u16(b13), u32(q2), u16(s2), u16(b2)]
+    outs = [np.zeros(H, np.float32) for _ in range(3)]
+    p, u, f = C.c_void_p, C.c_uint32, C.c_float
+    shim.miori_shim_test_ffn.argtypes = [p] * 9 + [u, u, f, p, p, p]
+    rc = shim.miori_shim_test_ffn(*[a.ctypes.data for a in arrs], gi.ctypes.data, gp.ctypes.data, x.ctypes.data,
+                                  F, H, 1e-5, *[o.ctypes.data for o in outs])
+    assert rc == 0, shim.miori_shim_last_error()
+    six, gated, normed_gated = outs
+    assert np.array_equal(six, gated), "the gated GEMV changes the block's result"
+    h = port.rmsnorm(x[None, :], gi, 1e-5)
+    y13 = port.gemv(4, arrs[0], arrs[1], arrs[2], h, 32)
+    act = port.silu_mul(np.ascontiguousarray(y13[:, :F]), np.ascontiguousarray(y13[:, F:]))
+    down = port.gemv(4, arrs[3], arrs[4], arrs[5], act, 32).astype(np.float32)
+    want = port.post_norm_add(x[None, :], down, gp, 1e-5)[0]
+    for name, got in (("six operators", six), ("norm + gated GEMV", normed_gated)):
+        rel = np.abs(got - want).max() / np.abs(want).max()
+        assert rel < 2e-3, f"{name}: max|d|/max|ref| = {rel:.2e}"
